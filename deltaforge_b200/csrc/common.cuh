@@ -1,0 +1,65 @@
+// Shared device helpers for the decode-step kernels (sm_100a).
+//
+// Rounding helpers mirror the places where the reference's torch expressions round to bf16, so the
+// fused kernels can keep those rounding points; see the per-kernel comments for which ones.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dfb {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float bf2f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ bf16 f2bf(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float round_bf16(float v) { return bf2f(f2bf(v)); }
+
+// x / (1 + exp(-x)) with the full-precision exponential, as torch evaluates SiLU in fp32.
+__device__ __forceinline__ float silu_f(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+// 1 / sqrt(x) as two correctly rounded steps, which is how a CPU evaluates rsqrt.
+__device__ __forceinline__ float rsqrt_2step(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+// log(1 + exp(x)) with torch's threshold of 20 above which softplus is the identity.
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Streaming loads for data read exactly once per step (weights, KV): no L1 allocation and an
+// evict-first L2 policy, so the activations, partial sums and recurrent state keep their L2 lines.
+__device__ __forceinline__ uint64_t make_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint2 ldg_stream_u2(const void* p, uint64_t pol) {
+  uint2 r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.u32 {%0,%1}, [%2], %3;"
+               : "=r"(r.x), "=r"(r.y)
+               : "l"(p), "l"(pol));
+  return r;
+}
+__device__ __forceinline__ uint4 ldg_stream_u4(const void* p, uint64_t pol) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p), "l"(pol));
+  return r;
+}
+
+// Error reporting shared by the C entry points (defined in abi.cu).
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+
+}  // namespace dfb

@@ -1,0 +1,435 @@
+// The whole single-token decode step as one launch sequence, captured into one CUDA graph.
+//
+// Stands in for ReferenceModel.forward at seq_len 1 plus the argmax of greedy_decode
+// (src/deltaforge/reference.py:779-817, src/deltaforge/model.py:141-147). Five launches per layer:
+//   1. RMSNorm-prologue int4 GEMV over the concatenated input projections
+//      (DeltaNet: in_proj_qkv|z|b|a with the causal conv + SiLU in the epilogue; attention: q|k|v)
+//   2. DeltaNet step, or attention prep (norms, RoPE, KV write) + split-KV decode (2 launches)
+//   3. out_proj / o_proj GEMV with the residual add in the epilogue
+//   4. RMSNorm-prologue GEMV over gate_proj|up_proj
+//   5. SwiGLU-prologue down_proj GEMV with the residual add in the epilogue
+// then the final-norm-prologue LM-head GEMV and the argmax. The position lives in device memory and
+// is advanced by the last node, so the same graph replays for every token.
+#include <new>
+#include <vector>
+
+#include "../../include/dfb200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dfb {
+
+int gemv_configure();
+int attn_configure();
+
+int configure_kernels() {
+  if (int rc = gemv_configure()) return rc;
+  return attn_configure();
+}
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, total;
+};
+
+size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
+size_t linear_counters(const dfb_linear& l, int rows) { return gemv_counter_count(rows, l.K, l.N, l.group) * 4; }
+
+Workspace plan(const dfb_model_desc& m) {
+  Workspace w = {};
+  const size_t B = (size_t)m.batch;
+  size_t max_proj = 0, max_part = 0, max_ctr = 0;
+  auto visit = [&](const dfb_linear& l) {
+    max_part = std::max(max_part, linear_partials(l, m.batch));
+    max_ctr = std::max(max_ctr, linear_counters(l, m.batch));
+  };
+  for (int i = 0; i < m.num_layers; ++i) {
+    const dfb_layer_desc& L = m.layers_host[i];
+    max_proj = std::max(max_proj, (size_t)L.in_proj.N);
+    visit(L.in_proj);
+    visit(L.out_proj);
+    visit(L.gate_up);
+    visit(L.down);
+  }
+  visit(m.head);
+  const size_t mixw = std::max((size_t)m.lin_v_heads * m.lin_dv, (size_t)m.hq * m.head_dim);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += align_up(bytes, 256);
+    return at;
+  };
+  w.h = take(B * m.hidden * 2);
+  w.proj = take(B * max_proj * 2);
+  w.mix = take(B * mixw * 2);
+  w.qout = take(B * m.hq * m.head_dim * 2);
+  w.gu = take(B * 2 * m.intermediate * 2);
+  w.partials = take(max_part);
+  w.counters = take(max_ctr);
+  w.attn = take(dfb_attn_scratch_bytes(m.batch, m.hq, m.hkv, m.head_dim, m.attn_splits));
+  w.am_val = take(B * 64 * 4);
+  w.am_idx = take(B * 64 * 4);
+  w.am_ctr = take(B * 4);
+  w.total = off;
+  return w;
+}
+
+struct Engine {
+  dfb_model_desc m;
+  std::vector<dfb_layer_desc> layers;
+  Workspace ws;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int launches = 0;
+
+  char* at(size_t off) const { return (char*)m.workspace + off; }
+
+  int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
+           long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
+    GemvParams p = {};
+    p.x = x;
+    p.x_stride = x_stride;
+    p.rows = m.batch;
+    p.packed = l.packed;
+    p.scale = l.scale;
+    p.scale_bf16 = l.scale_is_bf16;
+    p.K = l.K;
+    p.N = l.N;
+    p.group = l.group;
+    p.prologue = prologue;
+    p.norm_w = (const bf16*)norm_w;
+    p.eps = m.eps;
+    p.up = up;
+    p.up_stride = up_stride;
+    p.epilogue = epilogue;
+    p.out = out;
+    p.out_stride = out_stride;
+    p.residual = out;
+    p.res_stride = out_stride;
+    if (conv_layer) {
+      p.conv_state = (bf16*)conv_layer->conv_state;
+      p.conv_w = (const bf16*)conv_layer->conv_w;
+      p.conv_dim = 2 * m.lin_k_heads * m.lin_dk + m.lin_v_heads * m.lin_dv;
+    }
+    p.partials = (float*)at(ws.partials);
+    p.counters = (unsigned*)at(ws.counters);
+    p.math = m.math;
+    ++launches;
+    return launch_gemv(p, s);
+  }
+
+  int step(cudaStream_t s) {
+    launches = 0;
+    bf16* h = (bf16*)at(ws.h);
+    bf16* proj = (bf16*)at(ws.proj);
+    bf16* mix = (bf16*)at(ws.mix);
+    bf16* qout = (bf16*)at(ws.qout);
+    bf16* gu = (bf16*)at(ws.gu);
+    const int H = m.hidden, I = m.intermediate;
+    int rc = launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, h, s);
+    ++launches;
+    if (rc) return rc;
+    for (int i = 0; i < m.num_layers; ++i) {
+      const dfb_layer_desc& L = layers[i];
+      const long pstride = L.in_proj.N;
+      if (L.kind == DFB_LAYER_DELTANET) {
+        rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, EPI_CONV, proj, pstride, &L, s);
+        if (rc) return rc;
+        const int kd = m.lin_k_heads * m.lin_dk, vd = m.lin_v_heads * m.lin_dv;
+        DeltaNetParams d = {};
+        d.batch = m.batch;
+        d.num_k_heads = m.lin_k_heads;
+        d.num_v_heads = m.lin_v_heads;
+        d.dk = m.lin_dk;
+        d.dv = m.lin_dv;
+        d.q = proj;
+        d.k = proj + kd;
+        d.v = proj + 2 * kd;
+        d.z = proj + 2 * kd + vd;
+        d.b = proj + 2 * kd + 2 * vd;
+        d.a = proj + 2 * kd + 2 * vd + m.lin_v_heads;
+        d.row_stride = pstride;
+        d.a_log = L.a_log;
+        d.dt_bias = L.dt_bias;
+        d.norm_w = L.gnorm_w;
+        d.norm_w_bf16 = L.gnorm_w_is_bf16;
+        d.eps = m.eps;
+        d.state = L.recurrent;
+        d.out = mix;
+        d.out_stride = vd;
+        rc = launch_deltanet_step(d, s);
+        ++launches;
+        if (rc) return rc;
+        rc = gemv(L.out_proj, mix, vd, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+        if (rc) return rc;
+      } else {
+        rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, EPI_STORE, proj, pstride, nullptr, s);
+        if (rc) return rc;
+        const int d_ = m.head_dim;
+        const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
+        AttnPrepParams pp = {};
+        pp.batch = m.batch;
+        pp.hq = m.hq;
+        pp.hkv = m.hkv;
+        pp.d = d_;
+        pp.rotary_dim = m.rotary_dim;
+        pp.proj = proj;
+        pp.proj_stride = pstride;
+        pp.q_norm_w = (const bf16*)L.q_norm_w;
+        pp.k_norm_w = (const bf16*)L.k_norm_w;
+        pp.eps = m.eps;
+        pp.inv_freq = m.inv_freq;
+        pp.pos = m.pos;
+        pp.q_out = qout;
+        pp.kcache = (bf16*)L.kcache;
+        pp.vcache = (bf16*)L.vcache;
+        pp.kv_batch_stride = kvb;
+        pp.kv_head_stride = kvh;
+        pp.attn_output_gate = m.attn_output_gate;
+        pp.max_seq = m.max_seq;
+        rc = launch_attn_prep(pp, s);
+        ++launches;
+        if (rc) return rc;
+        AttnParams a = {};
+        a.batch = m.batch;
+        a.hq = m.hq;
+        a.hkv = m.hkv;
+        a.d = d_;
+        a.q = qout;
+        a.q_stride = (long)m.hq * d_;
+        a.qh_stride = d_;
+        a.kcache = (const bf16*)L.kcache;
+        a.vcache = (const bf16*)L.vcache;
+        a.kv_batch_stride = kvb;
+        a.kv_head_stride = kvh;
+        a.pos = m.pos;
+        a.scale = 1.0f / sqrtf((float)d_);
+        a.splits = m.attn_splits;
+        if (m.attn_splits > 1) {
+          char* sc = at(ws.attn);
+          a.part_acc = (float*)sc;
+          sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
+          a.part_ml = (float*)sc;
+          sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
+          a.counters = (unsigned*)sc;
+        }
+        if (m.attn_output_gate) {
+          a.gate = proj + d_;
+          a.gate_stride = pstride;
+          a.gateh_stride = 2 * d_;
+          a.gate_swish = m.gate_is_swish;
+        }
+        a.out = mix;
+        a.out_stride = (long)m.hq * d_;
+        rc = launch_attn_decode(a, s);
+        ++launches;
+        if (rc) return rc;
+        rc = gemv(L.out_proj, mix, (long)m.hq * d_, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+        if (rc) return rc;
+      }
+      rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
+      if (rc) return rc;
+      rc = gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
+      if (rc) return rc;
+    }
+    rc = gemv(m.head, h, H, PRO_RMSNORM, m.final_norm_w, nullptr, 0, EPI_STORE, (bf16*)m.logits, m.vocab, nullptr, s);
+    if (rc) return rc;
+    rc = launch_argmax((const bf16*)m.logits, m.batch, m.vocab, m.vocab, m.tokens, m.history, m.pos, (float*)at(ws.am_val),
+                       (int*)at(ws.am_idx), (unsigned*)at(ws.am_ctr), s);
+    ++launches;
+    if (rc) return rc;
+    rc = launch_advance(m.pos, 1, s);
+    ++launches;
+    return rc;
+  }
+};
+
+int validate(const dfb_model_desc& m) {
+  if (m.batch < 1 || m.num_layers < 0 || m.hidden < 1 || m.vocab < 1) {
+    set_error("engine: bad model shape");
+    return DFB_ERR_ARG;
+  }
+  if (!m.embed || !m.final_norm_w || !m.tokens || !m.pos || !m.logits || !m.workspace || !m.inv_freq ||
+      (m.num_layers && !m.layers_host)) {
+    set_error("engine: null pointer in the model description");
+    return DFB_ERR_ARG;
+  }
+  if (m.head.K != m.hidden || m.head.N != m.vocab) {
+    set_error("engine: LM head is %dx%d, expected %dx%d", m.head.N, m.head.K, m.vocab, m.hidden);
+    return DFB_ERR_ARG;
+  }
+  const int conv_dim = 2 * m.lin_k_heads * m.lin_dk + m.lin_v_heads * m.lin_dv;
+  for (int i = 0; i < m.num_layers; ++i) {
+    const dfb_layer_desc& L = m.layers_host[i];
+    int want_in, want_mix;
+    if (L.kind == DFB_LAYER_DELTANET) {
+      want_in = conv_dim + m.lin_v_heads * m.lin_dv + 2 * m.lin_v_heads;
+      want_mix = m.lin_v_heads * m.lin_dv;
+      if (!L.conv_w || !L.a_log || !L.dt_bias || !L.gnorm_w || !L.conv_state || !L.recurrent) {
+        set_error("engine: layer %d (DeltaNet) has a null pointer", i);
+        return DFB_ERR_ARG;
+      }
+    } else if (L.kind == DFB_LAYER_ATTENTION) {
+      want_in = m.hq * m.head_dim * (m.attn_output_gate ? 2 : 1) + 2 * m.hkv * m.head_dim;
+      want_mix = m.hq * m.head_dim;
+      if (!L.q_norm_w || !L.k_norm_w || !L.kcache || !L.vcache) {
+        set_error("engine: layer %d (attention) has a null pointer", i);
+        return DFB_ERR_ARG;
+      }
+    } else {
+      set_error("engine: layer %d has unknown kind %d", i, L.kind);
+      return DFB_ERR_ARG;
+    }
+    if (L.in_proj.K != m.hidden || L.in_proj.N != want_in || L.out_proj.K != want_mix || L.out_proj.N != m.hidden ||
+        L.gate_up.K != m.hidden || L.gate_up.N != 2 * m.intermediate || L.down.K != m.intermediate ||
+        L.down.N != m.hidden) {
+      set_error("engine: layer %d has a projection of the wrong shape", i);
+      return DFB_ERR_ARG;
+    }
+    if (!L.input_norm_w || !L.post_norm_w) {
+      set_error("engine: layer %d lacks a norm weight", i);
+      return DFB_ERR_ARG;
+    }
+  }
+  return DFB_OK;
+}
+
+}  // namespace
+}  // namespace dfb
+
+using namespace dfb;
+
+extern "C" {
+
+size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc) {
+  if (!desc || (desc->num_layers && !desc->layers_host)) return 0;
+  return plan(*desc).total;
+}
+
+int dfb_engine_create(const dfb_model_desc* desc, void** engine_out) {
+  if (!desc || !engine_out) {
+    set_error("dfb_engine_create: null argument");
+    return DFB_ERR_ARG;
+  }
+  if (int rc = validate(*desc)) return rc;
+  const Workspace w = plan(*desc);
+  if (desc->workspace_bytes < w.total) {
+    set_error("engine: workspace of %zu bytes required, got %zu", w.total, desc->workspace_bytes);
+    return DFB_ERR_ARG;
+  }
+  if (int rc = configure_kernels()) return rc;
+  Engine* e = new (std::nothrow) Engine();
+  if (!e) {
+    set_error("engine: out of host memory");
+    return DFB_ERR_ARG;
+  }
+  e->m = *desc;
+  e->layers.assign(desc->layers_host, desc->layers_host + desc->num_layers);
+  e->m.layers_host = e->layers.data();
+  e->ws = w;
+  *engine_out = e;
+  return DFB_OK;
+}
+
+int dfb_engine_destroy(void* engine) {
+  Engine* e = (Engine*)engine;
+  if (!e) return DFB_OK;
+  if (e->exec) cudaGraphExecDestroy(e->exec);
+  if (e->graph) cudaGraphDestroy(e->graph);
+  delete e;
+  return DFB_OK;
+}
+
+int dfb_engine_step(void* engine, void* stream) {
+  if (!engine) {
+    set_error("dfb_engine_step: null engine");
+    return DFB_ERR_ARG;
+  }
+  return ((Engine*)engine)->step((cudaStream_t)stream);
+}
+
+int dfb_engine_capture(void* engine, void* stream) {
+  Engine* e = (Engine*)engine;
+  if (!e) {
+    set_error("dfb_engine_capture: null engine");
+    return DFB_ERR_ARG;
+  }
+  if (e->exec) {
+    cudaGraphExecDestroy(e->exec);
+    e->exec = nullptr;
+  }
+  if (e->graph) {
+    cudaGraphDestroy(e->graph);
+    e->graph = nullptr;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t ce = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+  if (ce != cudaSuccess) {
+    set_error("engine: cannot begin stream capture: %s", cudaGetErrorString(ce));
+    return DFB_ERR_CUDA;
+  }
+  const int rc = e->step(s);
+  ce = cudaStreamEndCapture(s, &e->graph);
+  if (rc) return rc;
+  if (ce != cudaSuccess) {
+    set_error("engine: stream capture failed: %s", cudaGetErrorString(ce));
+    return DFB_ERR_CUDA;
+  }
+  ce = cudaGraphInstantiate(&e->exec, e->graph, 0);
+  if (ce != cudaSuccess) {
+    set_error("engine: graph instantiation failed: %s", cudaGetErrorString(ce));
+    return DFB_ERR_CUDA;
+  }
+  return DFB_OK;
+}
+
+int dfb_engine_replay(void* engine, int steps, void* stream) {
+  Engine* e = (Engine*)engine;
+  if (!e || !e->exec) {
+    set_error("dfb_engine_replay: no captured graph");
+    return DFB_ERR_ARG;
+  }
+  for (int i = 0; i < steps; ++i) {
+    const cudaError_t ce = cudaGraphLaunch(e->exec, (cudaStream_t)stream);
+    if (ce != cudaSuccess) {
+      set_error("engine: graph launch failed: %s", cudaGetErrorString(ce));
+      return DFB_ERR_CUDA;
+    }
+  }
+  return DFB_OK;
+}
+
+int dfb_engine_decode_host(void* engine, const int64_t* tokens_host, int steps, int64_t* out_host, void* stream) {
+  Engine* e = (Engine*)engine;
+  if (!e || !e->exec) {
+    set_error("dfb_engine_decode_host: no captured graph");
+    return DFB_ERR_ARG;
+  }
+  if (!tokens_host || !out_host) {
+    set_error("dfb_engine_decode_host: null host buffer");
+    return DFB_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t bytes = (size_t)e->m.batch * sizeof(int64_t);
+  const int64_t* src = tokens_host;
+  for (int i = 0; i < steps; ++i) {
+    cudaError_t ce = cudaMemcpyAsync(e->m.tokens, src, bytes, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess) ce = cudaGraphLaunch(e->exec, s);
+    int64_t* dst = out_host + (size_t)i * e->m.batch;
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(dst, e->m.tokens, bytes, cudaMemcpyDeviceToHost, s);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(s);
+    if (ce != cudaSuccess) {
+      set_error("engine: decode step %d failed: %s", i, cudaGetErrorString(ce));
+      return DFB_ERR_CUDA;
+    }
+    src = dst;
+  }
+  return DFB_OK;
+}
+
+int dfb_engine_launches_per_step(void* engine) { return engine ? ((Engine*)engine)->launches : 0; }
+
+}  // extern "C"

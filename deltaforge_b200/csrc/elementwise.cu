@@ -1,0 +1,215 @@
+// Small elementwise kernels of the decode step, sm_100a: the standalone forms of operations that the
+// fused kernels otherwise absorb. Each keeps the rounding points of the reference op it stands for.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dfb {
+
+namespace {
+
+// y = bf16(x * rsqrt(mean(x^2) + eps) * (1 + w)); optionally x = bf16(x + residual) first.
+// src/deltaforge/reference.py:92-96; src/deltaforge/kernels/fused_rmsnorm_residual.py:56-111.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* x, const bf16* res, const bf16* w, float eps, int n,
+                                                       bf16* resid_out, bf16* out) {
+  __shared__ float wred[8];
+  const long row = blockIdx.x;
+  const bf16* xr = x + row * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += 256) {
+    float v = bf2f(xr[i]);
+    if (res) {
+      v = round_bf16(__fadd_rn(bf2f(res[row * n + i]), v));
+      resid_out[row * n + i] = f2bf(v);
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += wred[i];
+  const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)n), eps));
+  for (int i = threadIdx.x; i < n; i += 256) {
+    const float v = res ? bf2f(resid_out[row * n + i]) : bf2f(xr[i]);
+    out[row * n + i] = f2bf(__fmul_rn(__fmul_rn(v, rstd), __fadd_rn(1.0f, bf2f(w[i]))));
+  }
+}
+
+// bf16(bf16(silu(gate)) * up). src/deltaforge/kernels/fused_swiglu.py:18-22, :37-48.
+__global__ void silu_mul_kernel(const bf16* gate, const bf16* up, long n, bf16* out) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float s = round_bf16(silu_f(bf2f(gate[i])));
+  out[i] = f2bf(__fmul_rn(s, bf2f(up[i])));
+}
+
+// x (batch, heads, seq, d), cos/sin (batch, seq, rd). src/deltaforge/reference.py:137-149.
+__global__ void partial_rope_kernel(const bf16* x, const bf16* cs, const bf16* sn, int heads, int seq, int d, int rd,
+                                    bf16* out) {
+  const long rowi = blockIdx.x;  // (b * heads + h) * seq + s
+  const int s = (int)(rowi % seq);
+  const int b = (int)(rowi / ((long)heads * seq));
+  const bf16* xr = x + rowi * d;
+  const bf16* c = cs + ((long)b * seq + s) * rd;
+  const bf16* sv = sn + ((long)b * seq + s) * rd;
+  const int half = rd / 2;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    if (i >= rd) {
+      out[rowi * d + i] = xr[i];
+      continue;
+    }
+    const float xo = (i < half) ? -bf2f(xr[i + half]) : bf2f(xr[i - half]);
+    const float a = round_bf16(__fmul_rn(bf2f(xr[i]), bf2f(c[i])));
+    const float r = round_bf16(__fmul_rn(xo, bf2f(sv[i])));
+    out[rowi * d + i] = f2bf(__fadd_rn(a, r));
+  }
+}
+
+// x (B, C), cache (B, C, 3) oldest first, w (C, 4). src/deltaforge/kernels/inline_causal_conv.py:98-129.
+__global__ void causal_conv_step_kernel(const bf16* x, bf16* cache, const bf16* w, int channels, long total, bf16* out) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = (int)(i % channels);
+  bf16* st = cache + i * 3;
+  const bf16* wc = w + (long)c * 4;
+  const bf16 xv = x[i];
+  float acc = __fmul_rn(bf2f(st[0]), bf2f(wc[0]));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(st[1]), bf2f(wc[1])));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(st[2]), bf2f(wc[2])));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(xv), bf2f(wc[3])));
+  out[i] = f2bf(silu_f(round_bf16(acc)));
+  st[0] = st[1];
+  st[1] = st[2];
+  st[2] = xv;
+}
+
+// Row gather of the embedding table (src/deltaforge/reference.py:804).
+__global__ void embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out) {
+  const int b = blockIdx.x;
+  const int64_t tok = tokens[b];
+  const uint4* src = (const uint4*)(table + tok * hidden);
+  uint4* dst = (uint4*)(out + (long)b * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+  for (int i = (hidden / 8) * 8 + threadIdx.x; i < hidden; i += blockDim.x) out[(long)b * hidden + i] = table[tok * hidden + i];
+}
+
+// argmax over a row of logits, first index on ties (what torch.argmax returns on the reference's CPU
+// path, src/deltaforge/model.py:142). Blocks reduce strided chunks, the last block to arrive reduces
+// the per-block results.
+constexpr int AM_BLOCKS = 64;
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) {
+    v = ov;
+    i = oi;
+  }
+}
+__global__ void __launch_bounds__(256) argmax_kernel(const bf16* logits, int n, long stride, int64_t* out, int64_t* hist,
+                                                     const int* pos, float* sval, int* sidx, unsigned* counter) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  __shared__ int s_last;
+  const int b = blockIdx.y;
+  const bf16* row = logits + (long)b * stride;
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += AM_BLOCKS * 256) argmax_merge(v, idx, bf2f(row[i]), i);
+  auto block_reduce = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      argmax_merge(v, idx, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) {
+      bv[threadIdx.x >> 5] = v;
+      bi[threadIdx.x >> 5] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int w = 1; w < 8; ++w) argmax_merge(v, idx, bv[w], bi[w]);
+  };
+  block_reduce();
+  if (threadIdx.x == 0) {
+    __stcg(&sval[b * AM_BLOCKS + blockIdx.x], v);
+    __stcg(&sidx[b * AM_BLOCKS + blockIdx.x], idx);
+    __threadfence();
+    const unsigned old = atomicAdd(&counter[b], 1u);
+    s_last = (old == AM_BLOCKS - 1);
+    if (s_last) counter[b] = 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  v = -INFINITY;
+  idx = 0x7fffffff;
+  if (threadIdx.x < AM_BLOCKS) {
+    v = __ldcg(&sval[b * AM_BLOCKS + threadIdx.x]);
+    idx = __ldcg(&sidx[b * AM_BLOCKS + threadIdx.x]);
+  }
+  __syncthreads();
+  block_reduce();
+  if (threadIdx.x == 0) {
+    out[b] = idx;
+    if (hist) hist[(long)(*pos) * gridDim.y + b] = idx;
+  }
+}
+
+__global__ void advance_kernel(int* pos, int by) { *pos += by; }
+
+}  // namespace
+
+int launch_rms_norm(const bf16* x, const bf16* w, float eps, int rows, int n, bf16* out, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  rms_norm_kernel<<<rows, 256, 0, s>>>(x, nullptr, w, eps, n, nullptr, out);
+  return check_launch("rms_norm");
+}
+
+int launch_add_rms_norm(const bf16* x, const bf16* res, const bf16* w, float eps, int rows, int n, bf16* resid_out,
+                        bf16* out, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  rms_norm_kernel<<<rows, 256, 0, s>>>(x, res, w, eps, n, resid_out, out);
+  return check_launch("add_rms_norm");
+}
+
+int launch_silu_mul(const bf16* gate, const bf16* up, long n, bf16* out, cudaStream_t s) {
+  if (n <= 0) return 0;
+  silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gate, up, n, out);
+  return check_launch("silu_mul");
+}
+
+int launch_partial_rope(const bf16* x, const bf16* cos, const bf16* sin, int batch, int heads, int seq, int d, int rd,
+                        bf16* out, cudaStream_t s) {
+  const long rows = (long)batch * heads * seq;
+  if (rows <= 0) return 0;
+  partial_rope_kernel<<<(unsigned)rows, 128, 0, s>>>(x, cos, sin, heads, seq, d, rd, out);
+  return check_launch("partial_rope");
+}
+
+int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch, int channels, bf16* out,
+                            cudaStream_t s) {
+  const long total = (long)batch * channels;
+  if (total <= 0) return 0;
+  causal_conv_step_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, cache, w, channels, total, out);
+  return check_launch("causal_conv_step");
+}
+
+int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s) {
+  if (batch <= 0) return 0;
+  embed_kernel<<<batch, 128, 0, s>>>(table, tokens, hidden, out);
+  return check_launch("embed");
+}
+
+int launch_argmax(const bf16* logits, int batch, int n, long stride, int64_t* out, int64_t* hist, const int* pos,
+                  float* scratch_val, int* scratch_idx, unsigned* counter, cudaStream_t s) {
+  if (batch <= 0) return 0;
+  argmax_kernel<<<dim3(AM_BLOCKS, batch), 256, 0, s>>>(logits, n, stride, out, hist, pos, scratch_val, scratch_idx, counter);
+  return check_launch("argmax");
+}
+
+int launch_advance(int* pos, int by, cudaStream_t s) {
+  advance_kernel<<<1, 1, 0, s>>>(pos, by);
+  return check_launch("advance");
+}
+
+}  // namespace dfb

@@ -1,0 +1,498 @@
+// Group-wise int4 dequant-GEMV for the decode step, sm_100a.
+//
+// Computes y[r, n] = sum_k x[r, k] * (nibble[k, n] - 8) * scale[k / group, n] on the weight layout
+// of the reference's K-major int4 format (src/deltaforge/kernels/tiled_gemv.py:242-288): packed is
+// [K/2, N] uint8 with N contiguous, byte [j, n] holds row j in its low nibble and row j + K/2 in
+// its high nibble, scale is [K/group, N]. It replaces the reference's Triton GEMV
+// (tiled_gemv.py:654-774, op deltaforge::tiled_gemv_int4 at :915-958) and the torch expression
+// torch_dequant_gemv_int4 (src/deltaforge/kernels/visible_int4_head.py:187-199).
+//
+// Fast path (group 128, K % 256 == 0, N % 8 == 0). One CTA of 256 threads owns a tile of 256
+// columns by 128 packed rows, i.e. exactly one scale group of the low half and one of the high
+// half. Each lane loads 8 bytes per row (a warp row is 256 contiguous bytes), each warp owns 16
+// rows, and all 16 loads of a thread are issued before anything else happens, so the whole tile is
+// in flight while the CTA builds its slice of the activation vector (with the RMSNorm or SwiGLU
+// prologue) in shared memory. Nibbles become fp16 values 1024 + n (or 1024 + 16 n for the high
+// nibble) by one logic op per pair, and are multiplied with the fp16 activation by the sm_100
+// mixed-precision FMA (f16 x f16 + f32), accumulating in fp32; the 1024 bias and the -8 zero point
+// are removed once per group from the activation sum, and the group's fp32 scale is applied once
+// per column. Warps are reduced through padded shared memory, split-K partial sums go to an fp32
+// scratch buffer, and the last CTA to arrive for a column tile adds them in fixed order (no
+// atomics on data, so results are identical run to run) and applies the epilogue: store, residual
+// add, or the DeltaNet causal-conv + SiLU step.
+//
+// Bytes per launch (what the roofline is computed from): K*N/2 packed + K/group*N scale bytes
+// + rows*N*2 output; the activation vector is re-read from L2 by every CTA and is not counted.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dfb {
+
+namespace {
+
+constexpr int TN = 256;             // columns per CTA
+constexpr int GROUP_ROWS = 128;     // packed rows per CTA = one scale group per half
+constexpr int NWARP = 8;
+constexpr int RPW = GROUP_ROWS / NWARP;  // rows per warp
+constexpr int PADW = TN + TN / 32;       // padded row of the cross-warp reduction buffer
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+  return r;
+}
+__device__ __forceinline__ float fma_f16(uint32_t pair, int hi, unsigned short x, float c) {
+  unsigned short a = hi ? (unsigned short)(pair >> 16) : (unsigned short)(pair & 0xffffu);
+  float d;
+  asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(x), "f"(c));
+  return d;
+}
+
+// Value of activation element k of row r after the prologue, as the bf16 the reference would hold.
+__device__ __forceinline__ float prologue_value(const GemvParams& p, int r, int k, float rstd) {
+  float xv = bf2f(p.x[(long)r * p.x_stride + k]);
+  if (p.prologue == PRO_RMSNORM) {
+    float v = __fmul_rn(xv, rstd);
+    v = __fmul_rn(v, __fadd_rn(1.0f, bf2f(p.norm_w[k])));
+    return round_bf16(v);
+  }
+  if (p.prologue == PRO_SILU_MUL) {
+    float s = round_bf16(silu_f(xv));
+    return round_bf16(__fmul_rn(s, bf2f(p.up[(long)r * p.up_stride + k])));
+  }
+  return xv;
+}
+
+// rsqrt(mean(x^2) + eps) of row r, computed by the whole CTA (blockDim.x threads, <= 32 warps).
+__device__ float cta_rstd(const GemvParams& p, int r, float* warp_scratch) {
+  float ss = 0.f;
+  for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+    float v = bf2f(p.x[(long)r * p.x_stride + k]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) warp_scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_scratch[w];
+  return rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
+}
+
+__device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
+  return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
+}
+
+// Output element (r, n) from its fp32 sum.
+__device__ __forceinline__ void epilogue_store(const GemvParams& p, int r, int n, float sum) {
+  bf16 y = f2bf(sum);
+  if (p.epilogue == EPI_RESIDUAL) {
+    float h = bf2f(p.residual[(long)r * p.res_stride + n]);
+    p.out[(long)r * p.out_stride + n] = f2bf(__fadd_rn(h, bf2f(y)));
+    return;
+  }
+  if (p.epilogue == EPI_CONV && n < p.conv_dim) {
+    // 4-tap depthwise causal conv decode step (src/deltaforge/kernels/inline_causal_conv.py:111-129):
+    // fp32 products summed left to right, rounded to bf16, then SiLU; history [h0,h1,h2] <- [h1,h2,x].
+    bf16* st = p.conv_state + ((long)r * p.conv_dim + n) * 3;
+    const bf16* w = p.conv_w + (long)n * 4;
+    float h0 = bf2f(st[0]), h1 = bf2f(st[1]), h2 = bf2f(st[2]), xv = bf2f(y);
+    float acc = __fmul_rn(h0, bf2f(w[0]));
+    acc = __fadd_rn(acc, __fmul_rn(h1, bf2f(w[1])));
+    acc = __fadd_rn(acc, __fmul_rn(h2, bf2f(w[2])));
+    acc = __fadd_rn(acc, __fmul_rn(xv, bf2f(w[3])));
+    float a = round_bf16(acc);
+    p.out[(long)r * p.out_stride + n] = f2bf(silu_f(a));
+    st[0] = st[1];
+    st[1] = st[2];
+    st[2] = y;
+    return;
+  }
+  p.out[(long)r * p.out_stride + n] = y;
+}
+
+template <int ROWS, int MATH>
+__global__ void __launch_bounds__(NWARP * 32) gemv_g128_kernel(const GemvParams p) {
+  extern __shared__ float smem[];
+  float* red = smem;                                  // [ROWS][2][NWARP][PADW]
+  float* xs_f = red + ROWS * 2 * NWARP * PADW;        // [ROWS][2][128] activation slice, fp32
+  __half* xs_h = (__half*)(xs_f + ROWS * 2 * 128);    // [ROWS][2][128] same, fp16
+  float* wsum = (float*)(xs_h + ROWS * 2 * 128);      // [ROWS][NWARP] per-warp activation sums
+  float* wscr = wsum + ROWS * NWARP;                  // [NWARP] scratch for the row statistic
+  __shared__ int s_last;
+
+  const int tile = blockIdx.x, g = blockIdx.y, zb = blockIdx.z;
+  const int G = p.K / 256, half = p.K / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  const int col0 = tile * TN + lane * 8;
+  const bool col_ok = col0 < p.N;
+  const int row0 = zb * ROWS;
+
+  // 1. Put this thread's 16 x 8 bytes of the weight tile in flight.
+  const uint64_t pol = make_evict_first_policy();
+  uint2 w[RPW];
+  {
+    const uint8_t* wp = p.packed + (size_t)(g * GROUP_ROWS + warp * RPW) * p.N + col0;
+#pragma unroll
+    for (int i = 0; i < RPW; ++i)
+      w[i] = col_ok ? ldg_stream_u2(wp + (size_t)i * p.N, pol) : make_uint2(0x88888888u, 0x88888888u);
+  }
+  float sL[8], sH[8];
+  if (MATH == MATH_EXACT) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      sL[c] = col_ok ? load_scale(p, (long)g * p.N + col0 + c) : 0.f;
+      sH[c] = col_ok ? load_scale(p, (long)(g + G) * p.N + col0 + c) : 0.f;
+    }
+  }
+
+  // 2. The 128 + 128 activation values this tile multiplies, after the prologue.
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int row = row0 + r;
+    float v = 0.f;
+    if (row < p.rows) {
+      float rstd = 1.f;
+      if (p.prologue == PRO_RMSNORM) rstd = cta_rstd(p, row, wscr);
+      const int kind = t >> 7, j = t & 127;
+      v = prologue_value(p, row, kind * half + g * GROUP_ROWS + j, rstd);
+    }
+    xs_f[r * 256 + t] = v;
+    __half hv = __float2half_rn(v);
+    xs_h[r * 256 + t] = hv;
+    float s = warp_sum(MATH == MATH_EXACT ? v : __half2float(hv));
+    if (lane == 0) wsum[r * NWARP + warp] = s;
+  }
+  __syncthreads();
+
+  // 3. Multiply-accumulate this warp's 16 rows.
+  float accL[ROWS][8], accH[ROWS][8];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) accL[r][c] = accH[r][c] = 0.f;
+
+  if (MATH == MATH_FAST) {
+    // ROWS == 1: the warp's 16 + 16 fp16 activations sit in registers (four 16-byte broadcast loads).
+    uint32_t xl[8], xh[8];
+    if (ROWS == 1) {
+      const uint4* xl4 = (const uint4*)(xs_h + warp * RPW);
+      const uint4* xh4 = (const uint4*)(xs_h + 128 + warp * RPW);
+      *(uint4*)&xl[0] = xl4[0];
+      *(uint4*)&xl[4] = xl4[1];
+      *(uint4*)&xh[0] = xh4[0];
+      *(uint4*)&xh[4] = xh4[1];
+    }
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+      uint32_t tq[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t wd = h ? w[i].y : w[i].x;
+        const uint32_t w8 = wd >> 8;
+        tq[h][0] = and_or(wd, 0x000F000Fu, 0x64006400u);  // bytes 0,2 low nibble : 1024 + n
+        tq[h][1] = and_or(wd, 0x00F000F0u, 0x64006400u);  // bytes 0,2 high nibble: 1024 + 16 n
+        tq[h][2] = and_or(w8, 0x000F000Fu, 0x64006400u);  // bytes 1,3 low
+        tq[h][3] = and_or(w8, 0x00F000F0u, 0x64006400u);  // bytes 1,3 high
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        unsigned short xlo, xhi;
+        if (ROWS == 1) {
+          xlo = (unsigned short)((i & 1) ? (xl[i >> 1] >> 16) : (xl[i >> 1] & 0xffffu));
+          xhi = (unsigned short)((i & 1) ? (xh[i >> 1] >> 16) : (xh[i >> 1] & 0xffffu));
+        } else {
+          xlo = __half_as_ushort(xs_h[r * 256 + warp * RPW + i]);
+          xhi = __half_as_ushort(xs_h[r * 256 + 128 + warp * RPW + i]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int b = h * 4;
+          accL[r][b + 0] = fma_f16(tq[h][0], 0, xlo, accL[r][b + 0]);
+          accL[r][b + 2] = fma_f16(tq[h][0], 1, xlo, accL[r][b + 2]);
+          accH[r][b + 0] = fma_f16(tq[h][1], 0, xhi, accH[r][b + 0]);
+          accH[r][b + 2] = fma_f16(tq[h][1], 1, xhi, accH[r][b + 2]);
+          accL[r][b + 1] = fma_f16(tq[h][2], 0, xlo, accL[r][b + 1]);
+          accL[r][b + 3] = fma_f16(tq[h][2], 1, xlo, accL[r][b + 3]);
+          accH[r][b + 1] = fma_f16(tq[h][3], 0, xhi, accH[r][b + 1]);
+          accH[r][b + 3] = fma_f16(tq[h][3], 1, xhi, accH[r][b + 3]);
+        }
+      }
+    }
+  } else if (MATH == MATH_FAST_HALF2) {
+    // Packed fp16 arithmetic: values are de-biased exactly, multiplied by the duplicated activation
+    // and summed in fp16 over 4 rows, then flushed to the fp32 accumulators.
+    const __half2 c1032 = __float2half2_rn(1032.f), c16th = __float2half2_rn(0.0625f), c72 = __float2half2_rn(72.f);
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+      for (int i0 = 0; i0 < RPW; i0 += 4) {
+        __half2 aL[4], aH[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) aL[q] = aH[q] = __float2half2_rn(0.f);
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii) {
+          const int i = i0 + ii;
+          const __half2 xlo = __half2half2(xs_h[r * 256 + warp * RPW + i]);
+          const __half2 xhi = __half2half2(xs_h[r * 256 + 128 + warp * RPW + i]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t wd = h ? w[i].y : w[i].x;
+            const uint32_t w8 = wd >> 8;
+            uint32_t t0 = and_or(wd, 0x000F000Fu, 0x64006400u), t1 = and_or(wd, 0x00F000F0u, 0x64006400u);
+            uint32_t t2 = and_or(w8, 0x000F000Fu, 0x64006400u), t3 = and_or(w8, 0x00F000F0u, 0x64006400u);
+            const __half2 q0 = __hsub2(*(__half2*)&t0, c1032), q1 = __hfma2(*(__half2*)&t1, c16th, __hneg2(c72));
+            const __half2 q2 = __hsub2(*(__half2*)&t2, c1032), q3 = __hfma2(*(__half2*)&t3, c16th, __hneg2(c72));
+            aL[h * 2 + 0] = __hfma2(q0, xlo, aL[h * 2 + 0]);
+            aH[h * 2 + 0] = __hfma2(q1, xhi, aH[h * 2 + 0]);
+            aL[h * 2 + 1] = __hfma2(q2, xlo, aL[h * 2 + 1]);
+            aH[h * 2 + 1] = __hfma2(q3, xhi, aH[h * 2 + 1]);
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int b = h * 4;
+          accL[r][b + 0] += __low2float(aL[h * 2]);
+          accL[r][b + 2] += __high2float(aL[h * 2]);
+          accL[r][b + 1] += __low2float(aL[h * 2 + 1]);
+          accL[r][b + 3] += __high2float(aL[h * 2 + 1]);
+          accH[r][b + 0] += __low2float(aH[h * 2]);
+          accH[r][b + 2] += __high2float(aH[h * 2]);
+          accH[r][b + 1] += __low2float(aH[h * 2 + 1]);
+          accH[r][b + 3] += __high2float(aH[h * 2 + 1]);
+        }
+      }
+    }
+  } else {
+    // Every weight is dequantised as the reference does it, bf16(fp32(nibble - 8) * fp32 scale),
+    // and multiplied with the activation in fp32.
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t byte = ((c < 4 ? w[i].x : w[i].y) >> (8 * (c & 3))) & 0xffu;
+        const float wl = round_bf16(__fmul_rn((float)((int)(byte & 15u) - 8), sL[c]));
+        const float wh = round_bf16(__fmul_rn((float)((int)(byte >> 4) - 8), sH[c]));
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          accL[r][c] = fmaf(xs_f[r * 256 + warp * RPW + i], wl, accL[r][c]);
+          accH[r][c] = fmaf(xs_f[r * 256 + 128 + warp * RPW + i], wh, accH[r][c]);
+        }
+      }
+    }
+  }
+
+  // 4. Reduce the 8 warps; column c of this thread goes to padded slot c + c/32 (conflict free both ways).
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int col = lane * 8 + c, slot = col + (col >> 5);
+      red[((r * 2 + 0) * NWARP + warp) * PADW + slot] = accL[r][c];
+      red[((r * 2 + 1) * NWARP + warp) * PADW + slot] = accH[r][c];
+    }
+  __syncthreads();
+
+  const int n = tile * TN + t;
+  const int slot = t + (t >> 5);
+  float val[ROWS];
+  {
+    float sl = 1.f, sh = 1.f;
+    if (MATH != MATH_EXACT && n < p.N) {
+      sl = load_scale(p, (long)g * p.N + n);
+      sh = load_scale(p, (long)(g + G) * p.N + n);
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      float vL = 0.f, vH = 0.f, sxL = 0.f, sxH = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < NWARP; ++wq) {
+        vL += red[((r * 2 + 0) * NWARP + wq) * PADW + slot];
+        vH += red[((r * 2 + 1) * NWARP + wq) * PADW + slot];
+      }
+#pragma unroll
+      for (int wq = 0; wq < 4; ++wq) {
+        sxL += wsum[r * NWARP + wq];
+        sxH += wsum[r * NWARP + 4 + wq];
+      }
+      if (MATH == MATH_FAST) {
+        // accL = sum x (1024 + n), accH = sum x (1024 + 16 n); remove the bias and the zero point 8.
+        vL = fmaf(-1032.f, sxL, vL);
+        vH = fmaf(-72.f, sxH, vH * 0.0625f);
+      }
+      val[r] = (MATH == MATH_EXACT) ? (vL + vH) : fmaf(sl, vL, sh * vH);
+    }
+  }
+
+  if (G == 1) {
+    if (n < p.N)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+        if (row0 + r < p.rows) epilogue_store(p, row0 + r, n, val[r]);
+    return;
+  }
+
+  // 5. Split-K: publish this group's partial, the last CTA of the column tile sums all groups in order.
+  if (n < p.N)
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+      if (row0 + r < p.rows) __stcg(&p.partials[((long)(row0 + r) * G + g) * p.N + n], val[r]);
+  __threadfence();
+  __syncthreads();
+  if (t == 0) {
+    unsigned* ctr = &p.counters[zb * gridDim.x + tile];
+    const unsigned old = atomicAdd(ctr, 1u);
+    s_last = (old == (unsigned)(G - 1));
+    if (s_last) *ctr = 0u;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (n < p.N)
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (row0 + r >= p.rows) break;
+      const float* pp = p.partials + (long)(row0 + r) * G * p.N + n;
+      float sum = 0.f;
+      for (int gg = 0; gg < G; ++gg) sum += __ldcg(pp + (long)gg * p.N);
+      epilogue_store(p, row0 + r, n, sum);
+    }
+}
+
+// Any K (even), any group that divides K/2, any N: one thread per column, weights dequantised as
+// the reference does. Used for shapes the fast path does not cover (toy models in the tests).
+__global__ void __launch_bounds__(128) gemv_generic_kernel(const GemvParams p) {
+  __shared__ float wscr[4];
+  const int r = blockIdx.y;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int half = p.K / 2;
+  float rstd = 1.f;
+  if (p.prologue == PRO_RMSNORM) rstd = cta_rstd(p, r, wscr);
+  if (n >= p.N) return;
+  float acc = 0.f;
+  for (int j = 0; j < half; ++j) {
+    const uint32_t byte = p.packed[(size_t)j * p.N + n];
+    const float sl = load_scale(p, (long)(j / p.group) * p.N + n);
+    const float sh = load_scale(p, (long)((j + half) / p.group) * p.N + n);
+    const float wl = round_bf16(__fmul_rn((float)((int)(byte & 15u) - 8), sl));
+    const float wh = round_bf16(__fmul_rn((float)((int)(byte >> 4) - 8), sh));
+    acc = fmaf(prologue_value(p, r, j, rstd), wl, acc);
+    acc = fmaf(prologue_value(p, r, j + half, rstd), wh, acc);
+  }
+  epilogue_store(p, r, n, acc);
+}
+
+__global__ void int4_unpack_kernel(const uint8_t* packed, int half, int N, int8_t* out) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)half * N) return;
+  const uint32_t byte = packed[idx];
+  out[idx] = (int8_t)((int)(byte & 15u) - 8);
+  out[idx + (long)half * N] = (int8_t)((int)(byte >> 4) - 8);
+}
+
+__global__ void int4_dequant_kernel(const uint8_t* packed, const void* scale, int scale_bf16, int half, int N, int group,
+                                    bf16* out) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)half * N) return;
+  const int j = (int)(idx / N), n = (int)(idx % N);
+  const uint32_t byte = packed[idx];
+  const long il = (long)(j / group) * N + n, ih = (long)((j + half) / group) * N + n;
+  const float sl = scale_bf16 ? bf2f(((const bf16*)scale)[il]) : ((const float*)scale)[il];
+  const float sh = scale_bf16 ? bf2f(((const bf16*)scale)[ih]) : ((const float*)scale)[ih];
+  out[idx] = f2bf(__fmul_rn((float)((int)(byte & 15u) - 8), sl));
+  out[idx + (long)half * N] = f2bf(__fmul_rn((float)((int)(byte >> 4) - 8), sh));
+}
+
+bool fast_path(const GemvParams& p) {
+  return p.group == 128 && p.K % 256 == 0 && p.N % 8 == 0 && ((uintptr_t)p.packed % 8) == 0;
+}
+
+template <int ROWS>
+size_t smem_bytes() {
+  return (size_t)ROWS * 2 * NWARP * PADW * 4 + (size_t)ROWS * 256 * 4 + (size_t)ROWS * 256 * 2 + (size_t)ROWS * NWARP * 4 +
+         NWARP * 4;
+}
+
+template <int ROWS, int MATH>
+int launch_fast(const GemvParams& p, cudaStream_t stream) {
+  const size_t smem = smem_bytes<ROWS>();
+  dim3 grid((p.N + TN - 1) / TN, p.K / 256, (p.rows + ROWS - 1) / ROWS);
+  gemv_g128_kernel<ROWS, MATH><<<grid, NWARP * 32, smem, stream>>>(p);
+  return check_launch("int4 gemv");
+}
+
+template <int ROWS>
+int launch_fast_math(const GemvParams& p, cudaStream_t stream) {
+  if (p.math == MATH_EXACT) return launch_fast<ROWS, MATH_EXACT>(p, stream);
+  if (p.math == MATH_FAST_HALF2) return launch_fast<ROWS, MATH_FAST_HALF2>(p, stream);
+  return launch_fast<ROWS, MATH_FAST>(p, stream);
+}
+
+}  // namespace
+
+template <int ROWS>
+static int configure_rows() {
+  const int smem = (int)smem_bytes<ROWS>();
+  cudaError_t e = cudaFuncSetAttribute(gemv_g128_kernel<ROWS, MATH_FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemv_g128_kernel<ROWS, MATH_EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemv_g128_kernel<ROWS, MATH_FAST_HALF2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  return e == cudaSuccess ? 0 : check_launch("int4 gemv: shared-memory opt-in");
+}
+
+int gemv_configure() {
+  if (int rc = configure_rows<1>()) return rc;
+  if (int rc = configure_rows<2>()) return rc;
+  return configure_rows<4>();
+}
+
+static int rows_per_cta(int rows) { return rows >= 4 ? 4 : (rows >= 2 ? 2 : 1); }
+
+size_t gemv_partials_bytes(int rows, int K, int N, int group) {
+  if (group != 128 || K % 256 != 0 || N % 8 != 0 || K / 256 < 2) return 0;
+  return (size_t)rows * (K / 256) * N * sizeof(float);
+}
+
+size_t gemv_counter_count(int rows, int K, int N, int group) {
+  if (group != 128 || K % 256 != 0 || N % 8 != 0) return 0;
+  const int rpc = rows_per_cta(rows);
+  return (size_t)((N + TN - 1) / TN) * ((rows + rpc - 1) / rpc);
+}
+
+int launch_gemv(const GemvParams& p, cudaStream_t stream) {
+  if (p.rows <= 0 || p.N <= 0) return 0;
+  static const int configured = gemv_configure();
+  if (configured) return configured;
+  if (fast_path(p)) {
+    if (p.K / 256 > 1 && (p.partials == nullptr || p.counters == nullptr)) {
+      set_error("int4 gemv: split-K scratch (partials, counters) is required for K=%d", p.K);
+      return 2;
+    }
+    switch (rows_per_cta(p.rows)) {
+      case 4: return launch_fast_math<4>(p, stream);
+      case 2: return launch_fast_math<2>(p, stream);
+      default: return launch_fast_math<1>(p, stream);
+    }
+  }
+  dim3 grid((p.N + 127) / 128, p.rows);
+  gemv_generic_kernel<<<grid, 128, 0, stream>>>(p);
+  return check_launch("int4 gemv (generic)");
+}
+
+int launch_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, cudaStream_t stream) {
+  const long total = (long)(K / 2) * N;
+  if (total == 0) return 0;
+  int4_unpack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(packed, K / 2, N, out);
+  return check_launch("int4 unpack");
+}
+
+int launch_int4_dequant(const uint8_t* packed, const void* scale, int scale_bf16, int K, int N, int group, bf16* out,
+                        cudaStream_t stream) {
+  const long total = (long)(K / 2) * N;
+  if (total == 0) return 0;
+  int4_dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(packed, scale, scale_bf16, K / 2, N, group, out);
+  return check_launch("int4 dequant");
+}
+
+}  // namespace dfb

@@ -1,0 +1,151 @@
+// Host-side launch interface of the decode-step kernels. Internal to the library: the public
+// surface is the C ABI in include/dfb200.h, whose entry points fill these structs.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dfb {
+
+typedef __nv_bfloat16 bf16;
+
+enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2 };
+// MATH_FAST sums x*q per scale group and applies the fp32 scale once per group (the weight is
+// never rounded to bf16); MATH_EXACT rounds every dequantised weight to bf16 before the product,
+// as the reference's expression does.
+enum Math { MATH_FAST = 0, MATH_EXACT = 1, MATH_FAST_HALF2 = 2 };
+
+struct GemvParams {
+  // activation, [rows, K] bf16
+  const bf16* x;
+  long x_stride;
+  int rows;
+  // weight: packed [K/2, N] uint8 (low nibble row j, high nibble row j + K/2), scale [K/group, N]
+  const uint8_t* packed;
+  const void* scale;
+  int scale_bf16;  // 0: fp32 scales, 1: bf16 scales
+  int K, N, group;
+  // prologue
+  int prologue;
+  const bf16* norm_w;  // PRO_RMSNORM: x <- bf16(x * rsqrt(mean(x^2) + eps) * (1 + norm_w))
+  float eps;
+  const bf16* up;  // PRO_SILU_MUL: x <- bf16(bf16(silu(x)) * up)
+  long up_stride;
+  // epilogue
+  int epilogue;
+  bf16* out;  // [rows, N]
+  long out_stride;
+  const bf16* residual;  // EPI_RESIDUAL: out <- bf16(residual + bf16(y)); may alias out
+  long res_stride;
+  bf16* conv_state;  // EPI_CONV: columns < conv_dim go through the 4-tap conv + SiLU, [rows, conv_dim, 3]
+  const bf16* conv_w;  // [conv_dim, 4]
+  int conv_dim;
+  // scratch: split-K partial sums [rows, K/256, N] fp32 and one arrival counter per column tile
+  float* partials;
+  unsigned* counters;
+  int math;
+};
+
+// Bytes of scratch the split-K path needs for a problem, and the number of counters.
+size_t gemv_partials_bytes(int rows, int K, int N, int group);
+size_t gemv_counter_count(int rows, int K, int N, int group);
+int launch_gemv(const GemvParams& p, cudaStream_t stream);
+
+int launch_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, cudaStream_t stream);
+int launch_int4_dequant(const uint8_t* packed, const void* scale, int scale_bf16, int K, int N, int group, bf16* out,
+                        cudaStream_t stream);
+
+struct DeltaNetParams {
+  int batch;
+  int num_k_heads, num_v_heads, dk, dv;  // dk == dv == 128 on the fast path
+  // post-conv activations, one row per sequence: q [Hk*dk], k [Hk*dk], v [Hv*dv] (bf16)
+  const bf16* q;
+  const bf16* k;
+  const bf16* v;
+  const bf16* z;  // gate of the output norm, [Hv*dv]
+  const bf16* b;  // [Hv] beta logits
+  const bf16* a;  // [Hv] decay logits
+  long row_stride;  // elements between sequences for q,k,v,z,b,a (they share one projection row)
+  const float* a_log;    // [Hv]
+  const float* dt_bias;  // [Hv]
+  const float* norm_w;   // [dv]
+  int norm_w_bf16;       // round norm_w * normed to bf16 (the weight is held in bf16 by the model)
+  float eps;
+  float* state;  // [batch, Hv, dk, dv] fp32, updated in place
+  bf16* out;     // [batch, Hv*dv]
+  long out_stride;
+};
+int launch_deltanet_step(const DeltaNetParams& p, cudaStream_t stream);
+
+struct DeltaRuleParams {  // the bare recurrence on pre-normalised q,k (fp32 in, fp32 out)
+  int batch, heads, dk, dv;
+  const float* state;
+  const float* q;
+  const float* k;
+  const float* v;
+  const float* g;
+  const float* beta;
+  float* out;
+  float* state_out;
+};
+int launch_delta_rule_step(const DeltaRuleParams& p, cudaStream_t stream);
+
+struct AttnParams {
+  int batch, hq, hkv, d;  // d == 256 on the fast path
+  const bf16* q;          // [batch, hq, d] (q_stride between sequences, qh_stride between heads)
+  long q_stride, qh_stride;
+  const bf16* kcache;  // [batch, hkv, max_seq, d]
+  const bf16* vcache;
+  long kv_batch_stride, kv_head_stride;  // elements; rows are d apart
+  int key_len;                            // used when pos == nullptr
+  const int* pos;                         // device scalar: key_len = *pos + 1
+  float scale;
+  int splits;
+  float* part_acc;  // [batch, hq, splits, d]
+  float* part_ml;   // [batch, hq, splits, 2]
+  unsigned* counters;  // [batch * hkv]
+  const bf16* gate;    // optional output-gate logits, one d-vector per query head
+  long gate_stride, gateh_stride;  // elements between sequences / between heads
+  int gate_swish;
+  bf16* out;  // [batch, hq*d]
+  long out_stride;
+};
+int launch_attn_decode(const AttnParams& p, cudaStream_t stream);
+
+struct AttnPrepParams {  // q/k RMSNorm + partial RoPE + KV-cache write for the new token
+  int batch, hq, hkv, d, rotary_dim;
+  const bf16* proj;  // [batch, hq*2*d (query|gate per head) + hkv*d (k) + hkv*d (v)]
+  long proj_stride;
+  const bf16* q_norm_w;
+  const bf16* k_norm_w;
+  float eps;
+  const float* inv_freq;  // [rotary_dim/2]
+  const int* pos;          // device scalar position
+  bf16* q_out;             // [batch, hq, d]
+  bf16* kcache;
+  bf16* vcache;
+  long kv_batch_stride, kv_head_stride;
+  int attn_output_gate;
+  int max_seq;  // rows per head in the cache; a position beyond it is not written
+};
+int launch_attn_prep(const AttnPrepParams& p, cudaStream_t stream);
+
+int launch_rms_norm(const bf16* x, const bf16* w, float eps, int rows, int n, bf16* out, cudaStream_t s);
+int launch_add_rms_norm(const bf16* x, const bf16* res, const bf16* w, float eps, int rows, int n, bf16* resid_out,
+                        bf16* out, cudaStream_t s);
+int launch_silu_mul(const bf16* gate, const bf16* up, long n, bf16* out, cudaStream_t s);
+int launch_partial_rope(const bf16* x, const bf16* cos, const bf16* sin, int batch, int heads, int seq, int d, int rd,
+                        bf16* out, cudaStream_t s);
+int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch, int channels, bf16* out,
+                            cudaStream_t s);
+int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s);
+// out[b] = argmax; optionally hist[*pos, b] = argmax. scratch_val/idx: [batch, 64]; counter: [batch], zeroed once.
+int launch_argmax(const bf16* logits, int batch, int n, long stride, int64_t* out, int64_t* hist, const int* pos,
+                  float* scratch_val, int* scratch_idx, unsigned* counter, cudaStream_t s);
+// Opt the kernels with large dynamic shared memory in; call once before stream capture.
+int configure_kernels();
+int launch_advance(int* pos, int by, cudaStream_t s);
+
+}  // namespace dfb

@@ -1,0 +1,273 @@
+/* dfb200 — C ABI of the B200 (sm_100a) int4 decode-step kernels.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless its name ends in
+ * `_host`. `stream` is a cudaStream_t passed as void* (NULL = the default stream). Every function
+ * returns 0 on success and a non-zero code otherwise (1 = CUDA error, 2 = bad argument); the text of
+ * the last error of the calling thread is returned by dfb_last_error(). Nothing here aborts, traps
+ * or falls back to a CPU path. The library allocates no device memory except CUDA graph objects
+ * owned by an engine: all buffers, including scratch, belong to the caller.
+ *
+ * Each entry point names the interface of LoveManna/deltaforge it stands in for (paths relative to
+ * that project's root). bf16 tensors are passed as void*, row-major with the last axis contiguous.
+ */
+#ifndef DFB200_H
+#define DFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFB_OK 0
+#define DFB_ERR_CUDA 1
+#define DFB_ERR_ARG 2
+
+/* Arithmetic of the int4 GEMV: FAST sums x*q per 128-group in fp32 and applies the group scale once
+ * (weights are not rounded to bf16); EXACT rounds every dequantised weight to bf16 first, exactly as
+ * torch_dequant_gemv_int4 does; FAST_HALF2 is FAST with packed fp16 partial sums. */
+#define DFB_MATH_FAST 0
+#define DFB_MATH_EXACT 1
+#define DFB_MATH_FAST_HALF2 2
+
+#define DFB_PROLOGUE_NONE 0
+#define DFB_PROLOGUE_RMSNORM 1  /* x <- rms_norm(x, norm_w, eps), reference.py:92-96 */
+#define DFB_PROLOGUE_SILU_MUL 2 /* x <- silu(x) * up, reference.py:692-693 */
+
+#define DFB_EPILOGUE_STORE 0
+#define DFB_EPILOGUE_RESIDUAL 1 /* out <- residual + y, reference.py:730,735 */
+#define DFB_EPILOGUE_CONV 2     /* columns < conv_dim: causal conv step + SiLU, reference.py:496-510 */
+
+const char* dfb_last_error(void);
+int dfb_abi_version(void);
+
+/* ---- int4, group-wise, K-major -------------------------------------------------------------- */
+
+/* packed [K/2, N] uint8 -> signed values [K, N] int8. The integer half of dequantise_int4_k_major,
+ * src/deltaforge/kernels/tiled_gemv.py:284-287. */
+int dfb_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, void* stream);
+
+/* packed + scale [K/group, N] -> bf16 weight [K, N] = bf16(fp32(value) * fp32(scale)).
+ * dequantise_int4_k_major followed by the cast in torch_dequant_gemv_int4:
+ * src/deltaforge/kernels/tiled_gemv.py:281-288, src/deltaforge/kernels/visible_int4_head.py:198. */
+int dfb_int4_dequant(const uint8_t* packed, const void* scale, int scale_is_bf16, int K, int N, int group,
+                     void* out_bf16, void* stream);
+
+typedef struct dfb_gemv_desc {
+  const void* x; /* bf16 [rows, K] */
+  int64_t x_stride;
+  int32_t rows;
+  const uint8_t* packed; /* [K/2, N] */
+  const void* scale;     /* [K/group, N], fp32 or bf16 */
+  int32_t scale_is_bf16;
+  int32_t K, N, group;
+  int32_t prologue;
+  const void* norm_w; /* bf16 [K] */
+  float eps;
+  const void* up; /* bf16 [rows, K] */
+  int64_t up_stride;
+  int32_t epilogue;
+  void* out; /* bf16 [rows, N] */
+  int64_t out_stride;
+  const void* residual; /* bf16 [rows, N]; may alias out */
+  int64_t residual_stride;
+  void* conv_state;   /* bf16 [rows, conv_dim, 3], oldest tap first, updated in place */
+  const void* conv_w; /* bf16 [conv_dim, 4] */
+  int32_t conv_dim;
+  void* scratch; /* dfb_int4_gemv_scratch_bytes() bytes; zero it once before first use */
+  size_t scratch_bytes;
+  int32_t math;
+} dfb_gemv_desc;
+
+/* Scratch for one GEMV problem: split-K partial sums followed by one arrival counter per column tile.
+ * The counters must be zero before the first launch; every launch leaves them zero again. */
+size_t dfb_int4_gemv_scratch_bytes(int rows, int K, int N, int group);
+
+/* y = x @ dequant(W), with optional fused prologue and epilogue. Stands in for the op
+ * deltaforge::tiled_gemv_int4(x, packed, scale, group_size) (src/deltaforge/kernels/tiled_gemv.py:
+ * 915-958) and torch_dequant_gemv_int4 (src/deltaforge/kernels/visible_int4_head.py:187-199); with
+ * the prologue/epilogue it also absorbs RMSNorm.forward (src/deltaforge/reference.py:92-96), the
+ * residual adds of DecoderLayer.forward (:730, :735), SwiGLUMLP's silu*up (:692-693) and the causal
+ * conv decode step (src/deltaforge/kernels/inline_causal_conv.py:98-129). */
+int dfb_int4_gemv(const dfb_gemv_desc* desc, void* stream);
+
+/* ---- elementwise ops with the reference's op contracts --------------------------------------- */
+
+/* deltaforge::rms_norm, src/deltaforge/kernels/fused_rmsnorm_residual.py:201-226. */
+int dfb_rms_norm(const void* x, const void* weight, float eps, int rows, int n, void* out, void* stream);
+/* deltaforge::add_rms_norm -> (resid_out = residual + x, out = rms_norm(resid_out)), :164-193. */
+int dfb_add_rms_norm(const void* x, const void* residual, const void* weight, float eps, int rows, int n,
+                     void* resid_out, void* out, void* stream);
+/* deltaforge::silu_mul, src/deltaforge/kernels/fused_swiglu.py:51-74. */
+int dfb_silu_mul(const void* gate, const void* up, int64_t n, void* out, void* stream);
+/* deltaforge::partial_rope: x (batch, heads, seq, d), cos/sin (batch, seq, rotary_dim).
+ * src/deltaforge/kernels/fused_rope.py:97-150. */
+int dfb_partial_rope(const void* x, const void* cos, const void* sin, int batch, int heads, int seq, int d,
+                     int rotary_dim, void* out, void* stream);
+/* deltaforge::fused_causal_conv_step: x (B, C), conv_cache (B, C, 3) updated in place, weight (C, 4).
+ * src/deltaforge/kernels/fused_causal_conv.py:136-176. */
+int dfb_causal_conv_step(const void* x, void* conv_cache, const void* weight, int batch, int channels, void* out,
+                         void* stream);
+
+/* ---- Gated DeltaNet ---------------------------------------------------------------------------- */
+
+/* deltaforge::delta_rule_step(state, q, k, v, g, beta) -> (out, new_state); all fp32, q and k already
+ * normalised. src/deltaforge/kernels/gated_delta_step.py:109-177. */
+int dfb_delta_rule_step(const float* state, const float* q, const float* k, const float* v, const float* g,
+                        const float* beta, int batch, int heads, int dk, int dv, float* out, float* state_out,
+                        void* stream);
+
+typedef struct dfb_deltanet_desc {
+  int32_t batch, num_k_heads, num_v_heads, dk, dv;
+  const void* q; /* bf16, post-conv, [Hk*dk] per sequence */
+  const void* k;
+  const void* v; /* [Hv*dv] */
+  const void* z; /* [Hv*dv] */
+  const void* b; /* [Hv] */
+  const void* a; /* [Hv] */
+  int64_t row_stride;
+  const float* a_log;
+  const float* dt_bias;
+  const float* norm_w;
+  int32_t norm_w_is_bf16; /* the model holds the norm weight in bf16: round weight*normed to bf16 */
+  float eps;
+  float* state; /* [batch, Hv, dk, dv], in place */
+  void* out;    /* bf16 [batch, Hv*dv] */
+  int64_t out_stride;
+} dfb_deltanet_desc;
+
+/* Everything of GatedDeltaNet.forward between the conv and out_proj for one token:
+ * src/deltaforge/reference.py:518-549 (l2norm :403-404, recurrence :450-458, GatedRMSNorm :115-121). */
+int dfb_deltanet_step(const dfb_deltanet_desc* desc, void* stream);
+
+/* ---- decode attention ---------------------------------------------------------------------------- */
+
+typedef struct dfb_attn_desc {
+  int32_t batch, hq, hkv, d;
+  const void* q; /* bf16 */
+  int64_t q_stride, qh_stride;
+  const void* kcache; /* bf16 [batch, hkv, max_seq, d] */
+  const void* vcache;
+  int64_t kv_batch_stride, kv_head_stride;
+  int32_t key_len;
+  const int32_t* pos; /* optional device scalar: key_len = *pos + 1 */
+  float scale;
+  int32_t splits;
+  void* scratch; /* dfb_attn_scratch_bytes(); zero once */
+  size_t scratch_bytes;
+  const void* gate; /* optional bf16 gate logits */
+  int64_t gate_stride, gateh_stride;
+  int32_t gate_is_swish;
+  void* out; /* bf16 [batch, hq*d] */
+  int64_t out_stride;
+} dfb_attn_desc;
+
+size_t dfb_attn_scratch_bytes(int batch, int hq, int hkv, int d, int splits);
+
+/* deltaforge::gqa_decode_attention(q, k, v, scale) (src/deltaforge/kernels/gqa_decode.py:138-199) when
+ * splits == 1 and deltaforge::split_kv_decode_attention(q, k, v, scale, splits)
+ * (src/deltaforge/kernels/flash_decode_splitkv.py:177-256) otherwise; with `gate` it also applies
+ * apply_output_gate (src/deltaforge/reference.py:558-568, :675-676). */
+int dfb_attn_decode(const dfb_attn_desc* desc, void* stream);
+
+typedef struct dfb_attn_prep_desc {
+  int32_t batch, hq, hkv, d, rotary_dim;
+  const void* proj; /* bf16 [batch, hq*(2d or d) + 2*hkv*d] */
+  int64_t proj_stride;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  float eps;
+  const float* inv_freq; /* [rotary_dim/2], as the model holds it */
+  const int32_t* pos;    /* device scalar */
+  void* q_out;           /* bf16 [batch, hq, d] */
+  void* kcache;
+  void* vcache;
+  int64_t kv_batch_stride, kv_head_stride;
+  int32_t attn_output_gate;
+  int32_t max_seq; /* rows per head of the cache; the caller keeps *pos below it */
+} dfb_attn_prep_desc;
+
+/* q_norm / k_norm, partial RoPE at *pos and the KV-cache write of GatedAttention.forward:
+ * src/deltaforge/reference.py:632-650. */
+int dfb_attn_prep(const dfb_attn_prep_desc* desc, void* stream);
+
+/* ---- whole decode step ------------------------------------------------------------------------- */
+
+typedef struct dfb_linear {
+  const uint8_t* packed;
+  const void* scale;
+  int32_t scale_is_bf16;
+  int32_t K, N, group;
+} dfb_linear;
+
+#define DFB_LAYER_DELTANET 0
+#define DFB_LAYER_ATTENTION 1
+
+typedef struct dfb_layer_desc {
+  int32_t kind;
+  const void* input_norm_w; /* bf16 [hidden] */
+  const void* post_norm_w;
+  dfb_linear in_proj;  /* DeltaNet: in_proj_qkv|z|b|a along N; attention: q_proj|k_proj|v_proj */
+  dfb_linear out_proj; /* out_proj / o_proj */
+  dfb_linear gate_up;  /* gate_proj|up_proj */
+  dfb_linear down;
+  const void* conv_w; /* bf16 [conv_dim, 4] */
+  const float* a_log;
+  const float* dt_bias;
+  const float* gnorm_w;
+  int32_t gnorm_w_is_bf16;
+  void* conv_state; /* bf16 [batch, conv_dim, 3] */
+  float* recurrent; /* [batch, Hv, dk, dv] */
+  const void* q_norm_w;
+  const void* k_norm_w;
+  void* kcache; /* bf16 [batch, hkv, max_seq, d] */
+  void* vcache;
+} dfb_layer_desc;
+
+typedef struct dfb_model_desc {
+  int32_t hidden, intermediate, vocab, num_layers, batch, max_seq;
+  int32_t hq, hkv, head_dim, rotary_dim, attn_output_gate, gate_is_swish;
+  int32_t lin_k_heads, lin_v_heads, lin_dk, lin_dv;
+  float eps;
+  const float* inv_freq;
+  const void* embed; /* bf16 [vocab, hidden] */
+  const void* final_norm_w;
+  dfb_linear head;
+  const dfb_layer_desc* layers_host; /* host array of num_layers entries, copied at creation */
+  int64_t* tokens;  /* [batch]: input token of the step, overwritten with the greedy next token */
+  int64_t* history; /* optional [max_seq, batch]: history[p] = token chosen after position p */
+  int32_t* pos;     /* device scalar: tokens already in the cache; the step advances it */
+  void* logits;     /* bf16 [batch, vocab] */
+  void* workspace;  /* dfb_engine_workspace_bytes(); zero once before creation */
+  size_t workspace_bytes;
+  int32_t attn_splits;
+  int32_t math;
+} dfb_model_desc;
+
+size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc);
+
+/* One engine = one model replica's decode step: ReferenceModel.forward at seq_len 1 plus the argmax of
+ * greedy_decode (src/deltaforge/reference.py:779-817, src/deltaforge/model.py:141-147). */
+int dfb_engine_create(const dfb_model_desc* desc, void** engine_out);
+int dfb_engine_destroy(void* engine);
+/* Enqueue the kernels of one step on `stream` (no graph). */
+int dfb_engine_step(void* engine, void* stream);
+/* Capture one step into a CUDA graph (the position is read from device memory, so one graph serves
+ * every token; the reference re-records per step, src/deltaforge/kernels/static_cache.py:62-74). */
+int dfb_engine_capture(void* engine, void* stream);
+/* Launch the captured step `steps` times back to back (greedy: each step consumes the token the
+ * previous one produced). */
+int dfb_engine_replay(void* engine, int steps, void* stream);
+/* Serving-style loop with host buffers: per step copy the input token host->device, run the graph,
+ * copy the chosen token device->host and wait for it. tokens_host holds [batch] input tokens on
+ * entry; out_host receives [steps, batch]. Both should be pinned for the copies to be asynchronous. */
+int dfb_engine_decode_host(void* engine, const int64_t* tokens_host, int steps, int64_t* out_host, void* stream);
+/* Number of kernel launches in one step. */
+int dfb_engine_launches_per_step(void* engine);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DFB200_H */
