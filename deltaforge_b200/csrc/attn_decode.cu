@@ -359,8 +359,9 @@ int launch_attn_decode(const AttnParams& p, cudaStream_t stream) {
       default: return launch_fast<8>(p, stream);
     }
   }
-  if (p.pos != nullptr) {
-    set_error("attention decode: the generic path needs key_len on the host");
+  // With a device-side position, key_len is the capacity of the cache (the most keys there can be).
+  if (p.key_len < 1) {
+    set_error("attention decode: the generic path needs key_len (or the cache capacity) on the host");
     return 2;
   }
   const size_t smem = (size_t)(p.d + p.key_len) * sizeof(float);

@@ -206,6 +206,7 @@ struct Engine {
         a.kv_batch_stride = kvb;
         a.kv_head_stride = kvh;
         a.pos = m.pos;
+        a.key_len = m.max_seq;  // capacity; the live length is *pos + 1
         a.scale = 1.0f / sqrtf((float)d_);
         a.splits = m.attn_splits;
         if (m.attn_splits > 1) {

@@ -166,8 +166,8 @@ class _Attention(nn.Module):
             v = v.repeat_interleave(groups, dim=1)
         scores = torch.matmul(q, k.transpose(2, 3)) * (d**-0.5)
         if t > 1:
-            qpos = torch.arange(t) + offset
-            blocked = torch.arange(k.shape[2]).unsqueeze(0) > qpos.unsqueeze(1)
+            qpos = torch.arange(t, device=scores.device) + offset
+            blocked = torch.arange(k.shape[2], device=scores.device).unsqueeze(0) > qpos.unsqueeze(1)
             scores = scores.masked_fill(blocked, torch.finfo(scores.dtype).min)
         w = F.softmax(scores, dim=-1, dtype=torch.float32).to(q.dtype)
         attn = torch.matmul(w, v).transpose(1, 2).reshape(b, t, -1)

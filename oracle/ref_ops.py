@@ -241,7 +241,7 @@ def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, i
     q = q / math.sqrt(q.shape[-1])
     b, h, t, dk = k.shape
     dv = v.shape[-1]
-    state = torch.zeros((b, h, dk, dv), dtype=torch.float32) if initial_state is None else initial_state.float()
+    state = torch.zeros((b, h, dk, dv), dtype=torch.float32, device=v.device) if initial_state is None else initial_state.float()
     out = torch.zeros_like(v)
     for i in range(t):
         out[:, :, i], state = delta_rule_step(state, q[:, :, i], k[:, :, i], v[:, :, i], g[:, :, i], beta[:, :, i])
