@@ -21,7 +21,8 @@ class GemvDesc(C.Structure):
         ("prologue", c_i32), ("norm_w", c_vp), ("eps", c_f32), ("up", c_vp), ("up_stride", c_i64),
         ("epilogue", c_i32), ("out", c_vp), ("out_stride", c_i64), ("residual", c_vp), ("residual_stride", c_i64),
         ("conv_state", c_vp), ("conv_w", c_vp), ("conv_dim", c_i32),
-        ("scratch", c_vp), ("scratch_bytes", c_sz), ("math", c_i32),
+        ("scratch", c_vp), ("scratch_bytes", c_sz), ("math", c_i32), ("force_tiled", c_i32),
+        ("packed_k8", c_vp),
     ]  # fmt: skip
 
 
@@ -56,7 +57,10 @@ class AttnPrepDesc(C.Structure):
 
 
 class Linear(C.Structure):
-    _fields_ = [("packed", c_vp), ("scale", c_vp), ("scale_is_bf16", c_i32), ("K", c_i32), ("N", c_i32), ("group", c_i32)]
+    _fields_ = [
+        ("packed", c_vp), ("scale", c_vp), ("scale_is_bf16", c_i32), ("K", c_i32), ("N", c_i32), ("group", c_i32),
+        ("packed_k8", c_vp),
+    ]  # fmt: skip
 
 
 class LayerDesc(C.Structure):
@@ -87,6 +91,7 @@ SIGNATURES = {
     "dfb_abi_version": (C.c_int, []),
     "dfb_int4_unpack": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_dequant": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_int, C.c_int, c_vp, c_vp]),
+    "dfb_int4_repack_k8": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_gemv_scratch_bytes": (c_sz, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "dfb_int4_gemv": (C.c_int, [C.POINTER(GemvDesc), c_vp]),
     "dfb_rms_norm": (C.c_int, [c_vp, c_vp, c_f32, C.c_int, C.c_int, c_vp, c_vp]),
@@ -106,6 +111,7 @@ SIGNATURES = {
     "dfb_engine_capture": (C.c_int, [c_vp, c_vp]),
     "dfb_engine_replay": (C.c_int, [c_vp, C.c_int, c_vp]),
     "dfb_engine_decode_host": (C.c_int, [c_vp, c_vp, C.c_int, c_vp, c_vp]),
+    "dfb_engine_status": (C.c_int, [c_vp, C.POINTER(C.c_int), c_vp]),
     "dfb_engine_launches_per_step": (C.c_int, [c_vp]),
 }
 

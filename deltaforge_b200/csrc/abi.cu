@@ -63,9 +63,16 @@ int dfb_int4_dequant(const uint8_t* packed, const void* scale, int scale_is_bf16
   return launch_int4_dequant(packed, scale, scale_is_bf16, K, N, group, (bf16*)out_bf16, (cudaStream_t)stream);
 }
 
+int dfb_int4_repack_k8(const uint8_t* packed, int K, int N, void* out, void* stream) {
+  if (!packed || !out) return bad("dfb_int4_repack_k8: null pointer");
+  if (K <= 0 || K % 8 || N <= 0) return bad("dfb_int4_repack_k8: K must be a positive multiple of 8, got K=%d N=%d", K, N);
+  return launch_int4_repack_k8(packed, K, N, (uint32_t*)out, (cudaStream_t)stream);
+}
+
 size_t dfb_int4_gemv_scratch_bytes(int rows, int K, int N, int group) {
   if (rows <= 0 || K <= 0 || N <= 0) return 0;
-  return align_up(gemv_partials_bytes(rows, K, N, group), 256) + align_up(gemv_counter_count(rows, K, N, group) * 4, 256);
+  const size_t body = align_up(gemv_partials_bytes(rows, K, N, group), 256) + align_up(gemv_counter_count(rows, K, N, group) * 4, 256);
+  return body ? body + 256 : 0;  // the last 256 bytes start with the status word
 }
 
 int dfb_int4_gemv(const dfb_gemv_desc* d, void* stream) {
@@ -112,7 +119,10 @@ int dfb_int4_gemv(const dfb_gemv_desc* d, void* stream) {
   if (need) {
     p.partials = (float*)d->scratch;
     p.counters = (unsigned*)((char*)d->scratch + align_up(gemv_partials_bytes(d->rows, d->K, d->N, d->group), 256));
+    p.status = (int*)((char*)d->scratch + need - 256);
   }
+  p.force_tiled = d->force_tiled;
+  p.packed_k8 = (const uint32_t*)d->packed_k8;
   return launch_gemv(p, (cudaStream_t)stream);
 }
 

@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(AW * 32) attn_decode_kernel(const AttnParams p
   float* wgt_s = ml_s + AW * GROUPS * 2;   // [GROUPS][MAX_SPLITS] merge weights
   __shared__ int s_last;
 
+  pdl_launch_dependents();
+  pdl_wait();  // q, the new K/V row and the position come from the kernels before this one
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const int L = p.pos ? (*p.pos + 1) : p.key_len;
@@ -210,6 +212,8 @@ __global__ void __launch_bounds__(AW * 32) attn_decode_kernel(const AttnParams p
 // Any head_dim and group size: one CTA of 128 threads per (query head, batch), one pass, no splits.
 __global__ void __launch_bounds__(128) attn_decode_generic_kernel(const AttnParams p) {
   extern __shared__ float sm[];  // [d] query, [L] scores
+  pdl_launch_dependents();
+  pdl_wait();
   const int hq = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
   const int groups = p.hq / p.hkv, hk = hq / groups, d = p.d;
   const int L = p.pos ? (*p.pos + 1) : p.key_len;
@@ -258,6 +262,8 @@ __global__ void __launch_bounds__(128) attn_decode_generic_kernel(const AttnPara
 // One warp per head row of the fused q|k|v projection.
 __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();  // the projection row comes from the GEMV before this kernel
   const int head = blockIdx.x * 4 + warp, b = blockIdx.y;
   const int total = p.hq + 2 * p.hkv;
   if (head >= total) return;
@@ -322,7 +328,8 @@ cudaError_t configure_groups() {
 template <int GROUPS>
 int launch_fast(const AttnParams& p, cudaStream_t stream) {
   const size_t smem = fast_smem<GROUPS>();
-  attn_decode_kernel<GROUPS><<<dim3(p.splits, p.hkv, p.batch), AW * 32, smem, stream>>>(p);
+  if (launch_pdl(attn_decode_kernel<GROUPS>, dim3(p.splits, p.hkv, p.batch), dim3(AW * 32), smem, stream, p) != cudaSuccess)
+    return check_launch("attention decode");
   return check_launch("attention decode");
 }
 
@@ -369,7 +376,8 @@ int launch_attn_decode(const AttnParams& p, cudaStream_t stream) {
     set_error("attention decode: generic path limited to %d keys", (int)(200 * 1024 / 4 - p.d));
     return 2;
   }
-  attn_decode_generic_kernel<<<dim3(p.hq, p.batch), 128, smem, stream>>>(p);
+  if (launch_pdl(attn_decode_generic_kernel, dim3(p.hq, p.batch), dim3(128), smem, stream, p) != cudaSuccess)
+    return check_launch("attention decode (generic)");
   return check_launch("attention decode (generic)");
 }
 
@@ -380,7 +388,8 @@ int launch_attn_prep(const AttnPrepParams& p, cudaStream_t stream) {
     return 2;
   }
   const int total = p.hq + 2 * p.hkv;
-  attn_prep_kernel<<<dim3((total + 3) / 4, p.batch), 128, 0, stream>>>(p);
+  if (launch_pdl(attn_prep_kernel, dim3((total + 3) / 4, p.batch), dim3(128), 0, stream, p) != cudaSuccess)
+    return check_launch("attention prep");
   return check_launch("attention prep");
 }
 

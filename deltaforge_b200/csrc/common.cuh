@@ -58,8 +58,31 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void* p, uint64_t pol) {
   return r;
 }
 
+// Programmatic dependent launch: a kernel that opens with pdl_prologue() lets its successor in the
+// stream start early and then waits until everything its predecessors wrote is visible. Without the
+// launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Error reporting shared by the C entry points (defined in abi.cu).
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
+
+// Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait()
+// before it reads or writes anything an earlier kernel of the stream touches).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace dfb

@@ -32,7 +32,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -73,6 +73,7 @@ Workspace plan(const dfb_model_desc& m) {
   w.am_val = take(B * 64 * 4);
   w.am_idx = take(B * 64 * 4);
   w.am_ctr = take(B * 4);
+  w.status = take(256);
   w.total = off;
   return w;
 }
@@ -94,6 +95,7 @@ struct Engine {
     p.x_stride = x_stride;
     p.rows = m.batch;
     p.packed = l.packed;
+    p.packed_k8 = (const uint32_t*)l.packed_k8;
     p.scale = l.scale;
     p.scale_bf16 = l.scale_is_bf16;
     p.K = l.K;
@@ -117,6 +119,7 @@ struct Engine {
     p.partials = (float*)at(ws.partials);
     p.counters = (unsigned*)at(ws.counters);
     p.math = m.math;
+    p.status = (int*)at(ws.status);
     ++launches;
     return launch_gemv(p, s);
   }
@@ -427,6 +430,21 @@ int dfb_engine_decode_host(void* engine, const int64_t* tokens_host, int steps, 
       return DFB_ERR_CUDA;
     }
     src = dst;
+  }
+  return DFB_OK;
+}
+
+int dfb_engine_status(void* engine, int* status_host, void* stream) {
+  Engine* e = (Engine*)engine;
+  if (!e || !status_host) {
+    set_error("dfb_engine_status: null argument");
+    return DFB_ERR_ARG;
+  }
+  cudaError_t ce = cudaMemcpyAsync(status_host, e->at(e->ws.status), sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize((cudaStream_t)stream);
+  if (ce != cudaSuccess) {
+    set_error("engine: reading the status word failed: %s", cudaGetErrorString(ce));
+    return DFB_ERR_CUDA;
   }
   return DFB_OK;
 }

@@ -87,6 +87,10 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   const bool col_ok = col < p.dv;
   const int dk = p.dk, dv = p.dv;
 
+  // Under programmatic dependent launch this kernel may start while the projection GEMV before it is
+  // still running: let the next kernel start its own prefetch, and touch nothing the GEMV writes
+  // until griddepcontrol.wait below. The recurrent state is only ever written by this kernel.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // 1. The state slab goes in flight first; nothing below depends on it until delta_core.
   float* S = p.state + ((long)(b * p.num_v_heads + hv) * dk) * dv;
   float s[RPT];
@@ -96,6 +100,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     s[i] = (col_ok && k < dk) ? __ldcs(S + (long)k * dv + col) : 0.f;
   }
 
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // 2. q, k of the key head: fp32, L2-normalised, query scaled by 1/sqrt(dk).
   const long row = (long)b * p.row_stride;
   {
@@ -202,13 +207,15 @@ int launch_deltanet_step(const DeltaNetParams& p, cudaStream_t stream) {
   cfg.blockDim = dim3(DN_WARPS * 32, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nvb;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, deltanet_fused_kernel, p);
   if (e != cudaSuccess) {
     set_error("deltanet step: launch failed: %s", cudaGetErrorString(e));

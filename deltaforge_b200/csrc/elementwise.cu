@@ -86,6 +86,8 @@ __global__ void causal_conv_step_kernel(const bf16* x, bf16* cache, const bf16* 
 
 // Row gather of the embedding table (src/deltaforge/reference.py:804).
 __global__ void embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   const int64_t tok = tokens[b];
   const uint4* src = (const uint4*)(table + tok * hidden);
@@ -109,6 +111,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const bf16* logits, int n, 
   __shared__ float bv[8];
   __shared__ int bi[8];
   __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.y;
   const bf16* row = logits + (long)b * stride;
   float v = -INFINITY;
@@ -155,7 +159,10 @@ __global__ void __launch_bounds__(256) argmax_kernel(const bf16* logits, int n, 
   }
 }
 
-__global__ void advance_kernel(int* pos, int by) { *pos += by; }
+__global__ void advance_kernel(int* pos, int by) {
+  pdl_wait();  // the argmax before this kernel still reads the position
+  *pos += by;
+}
 
 }  // namespace
 
@@ -196,19 +203,21 @@ int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch
 
 int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s) {
   if (batch <= 0) return 0;
-  embed_kernel<<<batch, 128, 0, s>>>(table, tokens, hidden, out);
+  if (launch_pdl(embed_kernel, dim3(batch), dim3(128), 0, s, table, tokens, hidden, out) != cudaSuccess) return check_launch("embed");
   return check_launch("embed");
 }
 
 int launch_argmax(const bf16* logits, int batch, int n, long stride, int64_t* out, int64_t* hist, const int* pos,
                   float* scratch_val, int* scratch_idx, unsigned* counter, cudaStream_t s) {
   if (batch <= 0) return 0;
-  argmax_kernel<<<dim3(AM_BLOCKS, batch), 256, 0, s>>>(logits, n, stride, out, hist, pos, scratch_val, scratch_idx, counter);
+  if (launch_pdl(argmax_kernel, dim3(AM_BLOCKS, batch), dim3(256), 0, s, logits, n, stride, out, hist, pos, scratch_val, scratch_idx,
+                 counter) != cudaSuccess)
+    return check_launch("argmax");
   return check_launch("argmax");
 }
 
 int launch_advance(int* pos, int by, cudaStream_t s) {
-  advance_kernel<<<1, 1, 0, s>>>(pos, by);
+  if (launch_pdl(advance_kernel, dim3(1), dim3(1), 0, s, pos, by) != cudaSuccess) return check_launch("advance");
   return check_launch("advance");
 }
 

@@ -1,0 +1,71 @@
+// Prologue and epilogue arithmetic shared by the int4 GEMV kernels.
+#pragma once
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace dfb {
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+  return r;
+}
+
+// d = a * b + c with a, b fp16 (the selected half of `pair`, and x) and c, d fp32: the product of two
+// fp16 numbers is exact in fp32, so this is one rounding, like an fp32 FMA on converted operands.
+__device__ __forceinline__ float fma_f16(uint32_t pair, int hi, unsigned short x, float c) {
+  unsigned short a = hi ? (unsigned short)(pair >> 16) : (unsigned short)(pair & 0xffffu);
+  float d;
+  asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(x), "f"(c));
+  return d;
+}
+
+// Value of activation element k of row r after the prologue, as the bf16 the reference would hold.
+__device__ __forceinline__ float prologue_value(const GemvParams& p, int r, int k, float rstd) {
+  float xv = bf2f(p.x[(long)r * p.x_stride + k]);
+  if (p.prologue == PRO_RMSNORM) {
+    float v = __fmul_rn(xv, rstd);
+    v = __fmul_rn(v, __fadd_rn(1.0f, bf2f(p.norm_w[k])));
+    return round_bf16(v);
+  }
+  if (p.prologue == PRO_SILU_MUL) {
+    float s = round_bf16(silu_f(xv));
+    return round_bf16(__fmul_rn(s, bf2f(p.up[(long)r * p.up_stride + k])));
+  }
+  return xv;
+}
+
+__device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
+  return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
+}
+
+// Output element (r, n) from its fp32 sum.
+__device__ __forceinline__ void epilogue_store(const GemvParams& p, int r, int n, float sum) {
+  bf16 y = f2bf(sum);
+  if (p.epilogue == EPI_RESIDUAL) {
+    float h = bf2f(p.residual[(long)r * p.res_stride + n]);
+    p.out[(long)r * p.out_stride + n] = f2bf(__fadd_rn(h, bf2f(y)));
+    return;
+  }
+  if (p.epilogue == EPI_CONV && n < p.conv_dim) {
+    // 4-tap depthwise causal conv decode step (src/deltaforge/kernels/inline_causal_conv.py:111-129):
+    // fp32 products summed left to right, rounded to bf16, then SiLU; history [h0,h1,h2] <- [h1,h2,x].
+    bf16* st = p.conv_state + ((long)r * p.conv_dim + n) * 3;
+    const bf16* w = p.conv_w + (long)n * 4;
+    float h0 = bf2f(st[0]), h1 = bf2f(st[1]), h2 = bf2f(st[2]), xv = bf2f(y);
+    float acc = __fmul_rn(h0, bf2f(w[0]));
+    acc = __fadd_rn(acc, __fmul_rn(h1, bf2f(w[1])));
+    acc = __fadd_rn(acc, __fmul_rn(h2, bf2f(w[2])));
+    acc = __fadd_rn(acc, __fmul_rn(xv, bf2f(w[3])));
+    float a = round_bf16(acc);
+    p.out[(long)r * p.out_stride + n] = f2bf(silu_f(a));
+    st[0] = st[1];
+    st[1] = st[2];
+    st[2] = y;
+    return;
+  }
+  p.out[(long)r * p.out_stride + n] = y;
+}
+
+}  // namespace dfb

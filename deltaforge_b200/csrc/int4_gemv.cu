@@ -23,8 +23,9 @@
 //
 // Bytes per launch (what the roofline is computed from): K*N/2 packed + K/group*N scale bytes
 // + rows*N*2 output; the activation vector is re-read from L2 by every CTA and is not counted.
-#include "common.cuh"
-#include "kernels.h"
+#include <algorithm>
+
+#include "gemv_common.cuh"
 
 namespace dfb {
 
@@ -35,33 +36,6 @@ constexpr int GROUP_ROWS = 128;     // packed rows per CTA = one scale group per
 constexpr int NWARP = 8;
 constexpr int RPW = GROUP_ROWS / NWARP;  // rows per warp
 constexpr int PADW = TN + TN / 32;       // padded row of the cross-warp reduction buffer
-
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
-  return r;
-}
-__device__ __forceinline__ float fma_f16(uint32_t pair, int hi, unsigned short x, float c) {
-  unsigned short a = hi ? (unsigned short)(pair >> 16) : (unsigned short)(pair & 0xffffu);
-  float d;
-  asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(x), "f"(c));
-  return d;
-}
-
-// Value of activation element k of row r after the prologue, as the bf16 the reference would hold.
-__device__ __forceinline__ float prologue_value(const GemvParams& p, int r, int k, float rstd) {
-  float xv = bf2f(p.x[(long)r * p.x_stride + k]);
-  if (p.prologue == PRO_RMSNORM) {
-    float v = __fmul_rn(xv, rstd);
-    v = __fmul_rn(v, __fadd_rn(1.0f, bf2f(p.norm_w[k])));
-    return round_bf16(v);
-  }
-  if (p.prologue == PRO_SILU_MUL) {
-    float s = round_bf16(silu_f(xv));
-    return round_bf16(__fmul_rn(s, bf2f(p.up[(long)r * p.up_stride + k])));
-  }
-  return xv;
-}
 
 // rsqrt(mean(x^2) + eps) of row r, computed by the whole CTA (blockDim.x threads, <= 32 warps).
 __device__ float cta_rstd(const GemvParams& p, int r, float* warp_scratch) {
@@ -77,38 +51,6 @@ __device__ float cta_rstd(const GemvParams& p, int r, float* warp_scratch) {
   float tot = 0.f;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_scratch[w];
   return rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
-}
-
-__device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
-  return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
-}
-
-// Output element (r, n) from its fp32 sum.
-__device__ __forceinline__ void epilogue_store(const GemvParams& p, int r, int n, float sum) {
-  bf16 y = f2bf(sum);
-  if (p.epilogue == EPI_RESIDUAL) {
-    float h = bf2f(p.residual[(long)r * p.res_stride + n]);
-    p.out[(long)r * p.out_stride + n] = f2bf(__fadd_rn(h, bf2f(y)));
-    return;
-  }
-  if (p.epilogue == EPI_CONV && n < p.conv_dim) {
-    // 4-tap depthwise causal conv decode step (src/deltaforge/kernels/inline_causal_conv.py:111-129):
-    // fp32 products summed left to right, rounded to bf16, then SiLU; history [h0,h1,h2] <- [h1,h2,x].
-    bf16* st = p.conv_state + ((long)r * p.conv_dim + n) * 3;
-    const bf16* w = p.conv_w + (long)n * 4;
-    float h0 = bf2f(st[0]), h1 = bf2f(st[1]), h2 = bf2f(st[2]), xv = bf2f(y);
-    float acc = __fmul_rn(h0, bf2f(w[0]));
-    acc = __fadd_rn(acc, __fmul_rn(h1, bf2f(w[1])));
-    acc = __fadd_rn(acc, __fmul_rn(h2, bf2f(w[2])));
-    acc = __fadd_rn(acc, __fmul_rn(xv, bf2f(w[3])));
-    float a = round_bf16(acc);
-    p.out[(long)r * p.out_stride + n] = f2bf(silu_f(a));
-    st[0] = st[1];
-    st[1] = st[2];
-    st[2] = y;
-    return;
-  }
-  p.out[(long)r * p.out_stride + n] = y;
 }
 
 template <int ROWS, int MATH>
@@ -442,6 +384,8 @@ static int configure_rows() {
 }
 
 int gemv_configure() {
+  if (int rc = stream_configure()) return rc;
+  if (int rc = cluster_configure()) return rc;
   if (int rc = configure_rows<1>()) return rc;
   if (int rc = configure_rows<2>()) return rc;
   return configure_rows<4>();
@@ -450,20 +394,28 @@ int gemv_configure() {
 static int rows_per_cta(int rows) { return rows >= 4 ? 4 : (rows >= 2 ? 2 : 1); }
 
 size_t gemv_partials_bytes(int rows, int K, int N, int group) {
-  if (group != 128 || K % 256 != 0 || N % 8 != 0 || K / 256 < 2) return 0;
-  return (size_t)rows * (K / 256) * N * sizeof(float);
+  if (group != 128 || K % 256 != 0 || N % 8 != 0) return 0;
+  const size_t tiled = K / 256 < 2 ? 0 : (size_t)rows * (K / 256) * N * sizeof(float);
+  const size_t streamed = (rows == 1 && N % 16 == 0) ? stream_partials_bytes(K, N) : 0;
+  return std::max(tiled, streamed);
 }
 
 size_t gemv_counter_count(int rows, int K, int N, int group) {
   if (group != 128 || K % 256 != 0 || N % 8 != 0) return 0;
   const int rpc = rows_per_cta(rows);
-  return (size_t)((N + TN - 1) / TN) * ((rows + rpc - 1) / rpc);
+  const size_t tiled = (size_t)((N + TN - 1) / TN) * ((rows + rpc - 1) / rpc);
+  return std::max(tiled, stream_counter_count(K, N));
 }
 
 int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   if (p.rows <= 0 || p.N <= 0) return 0;
   static const int configured = gemv_configure();
   if (configured) return configured;
+  if (!p.force_tiled && p.status) {
+    // layer-sized matrices: one cluster per column tile; very wide ones (the LM head): persistent streaming
+    if (p.N < 65536 && cluster_path_ok(p)) return launch_gemv_cluster(p, p.status, stream);
+    if (p.partials && p.counters && stream_path_ok(p)) return launch_gemv_stream(p, p.status, stream);
+  }
   if (fast_path(p)) {
     if (p.K / 256 > 1 && (p.partials == nullptr || p.counters == nullptr)) {
       set_error("int4 gemv: split-K scratch (partials, counters) is required for K=%d", p.K);

@@ -1,0 +1,384 @@
+// Cluster int4 dequant-GEMV for the per-layer projections of batch-1 decode, sm_100a.
+//
+// Same function, arithmetic and re-packed weight layout as int4_gemv_stream.cu (the reference's
+// group-128 int4 linear, op deltaforge::tiled_gemv_int4, src/deltaforge/kernels/tiled_gemv.py:915-958),
+// shaped for matrices of 5 to 25 MB, where the time of a launch is its chain of dependent latencies,
+// not its bytes:
+//
+//  * One thread-block cluster per column tile (256 or 128 columns); the CTAs of the cluster split
+//    the tile's 128-row scale groups between them. Each CTA issues the TMA copies of ALL its units
+//    (weight words and the group's scale row) at once, before it waits for the previous kernel of
+//    the stream (griddepcontrol.wait): there is no ring to recycle, and under programmatic dependent
+//    launch the whole matrix is already in shared memory or in flight when the activation arrives.
+//  * After the wait: the activation slice of the CTA's groups is quantised to 16-bit integers with a
+//    per-group exponent (see int4_gemv_stream.cu), every thread runs four dp4a per 8 nibbles over
+//    its 4 columns and its share of the rows, row lanes are added through shared memory, and the
+//    CTAs of the cluster hand their column sums to the cluster's first CTA through distributed
+//    shared memory. One hardware cluster barrier later that CTA adds them in rank order and applies
+//    the epilogue. No global scratch, no atomics, no grid-wide dependency: results are identical run
+//    to run.
+//
+// The wait on each TMA barrier is bounded (about two seconds); a CTA whose wait gives up records a
+// code in the status word and still takes part in the cluster barrier, so its cluster never hangs.
+//
+// Bytes per launch: K*N/2 (words) + K/128*N scale bytes + N*2 output.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "gemv_common.cuh"
+
+namespace dfb {
+
+namespace {
+
+constexpr int CTHREADS = 256;  // consumer threads
+constexpr int THREADS = CTHREADS + 32;
+constexpr int UROWS = 16;      // word rows per unit = one 128-row scale group
+constexpr int MAX_CS = 8;      // portable cluster size limit
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// store a float into the shared memory of CTA `rank` of this cluster, at the address `local` has here
+__device__ __forceinline__ void dsmem_store(float* local, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+  asm("dp4a.u32.s32 %0, %1, %2, %0;" : "+r"(c) : "r"(a), "r"(b));
+  return c;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+  asm("dp4a.u32.u32 %0, %1, %2, %0;" : "+r"(c) : "r"(a), "r"(b));
+  return c;
+}
+
+struct ClusterArgs {
+  GemvParams p;
+  int cs;        // cluster size = CTAs per column tile
+  int max_units; // most groups any CTA of a cluster gets
+  int* status;
+};
+
+template <int TNW>
+__global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_constant__ CUtensorMap wmap,
+                                                               const __grid_constant__ CUtensorMap smap, const ClusterArgs a) {
+  constexpr int CQ = TNW / 4;          // column quads per tile
+  constexpr int RL = CTHREADS / CQ;    // row lanes
+  constexpr int RPT = UROWS / RL;      // word rows per thread per unit
+  constexpr int W_BYTES = UROWS * TNW * 4;
+  constexpr int STAGE = W_BYTES + TNW * 4;  // + one scale row (fp32 size; bf16 uses half of it)
+  extern __shared__ unsigned char smem_raw[];
+  const GemvParams& p = a.p;
+  const int G = p.K / 128;
+  unsigned char* stage0 = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // max_units * STAGE
+  unsigned char* xq = stage0 + (size_t)a.max_units * STAGE;        // [max_units*16][16] activation bytes for dp4a
+  int* mk = (int*)(xq + (size_t)a.max_units * UROWS * 16);         // [max_units*16] sum of m per word row
+  float* fg = (float*)(mk + a.max_units * UROWS);                  // [max_units] 2^e per group
+  float* red = fg + ((a.max_units + 3) & ~3);                      // [RL][TNW] row-lane partials
+  float* dsm = red + RL * TNW;                                     // [cs][TNW] column sums from every rank (used in rank 0)
+  uint64_t* full = (uint64_t*)(dsm + MAX_CS * TNW);                // [max_units]
+  float* wred = (float*)(full + a.max_units);                      // [8]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  const int cs = a.cs;
+  const int rank = (int)cluster_rank();
+  const int tile = blockIdx.x / cs;
+  const int g0 = (int)((long)rank * G / cs), g1 = (int)((long)(rank + 1) * G / cs);
+  const int nunits = g1 - g0;
+  const uint32_t scale_bytes = p.scale_bf16 ? TNW * 2 : TNW * 4;
+
+  if (t == 0) {
+    for (int s = 0; s < nunits; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  bool ok = true;
+  if (warp == CTHREADS / 32) {
+    // producer: everything this CTA will read from the weight, at once (weights never depend on earlier kernels)
+    if (lane == 0) {
+      const uint64_t pol = make_evict_first_policy();
+      for (int s = 0; s < nunits; ++s) {
+        unsigned char* dst = stage0 + (size_t)s * STAGE;
+        mbar_expect_tx(&full[s], W_BYTES + scale_bytes);
+        tma_load_2d(dst, &wmap, tile * TNW, (g0 + s) * UROWS, &full[s], pol);
+        tma_load_2d(dst + W_BYTES, &smap, tile * TNW, g0 + s, &full[s], pol);
+      }
+    }
+  } else {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
+    float rstd = 1.f;
+    if (p.prologue == PRO_RMSNORM) {
+      float ss = 0.f;
+      for (int k = t; k < p.K; k += CTHREADS) {
+        const float v = bf2f(p.x[k]);
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) wred[warp] = ss;
+      consumer_sync();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+      rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
+    }
+    // one warp per group of this CTA: shared exponent, 16-bit integers, bytes laid out for dp4a
+    for (int gl = warp; gl < nunits; gl += CTHREADS / 32) {
+      const int g = g0 + gl;
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = prologue_value(p, 0, g * 128 + lane * 4 + i, rstd);
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+      amax = warp_max(amax);
+      int E = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
+      E = max(E, -100);
+      const float up = __uint_as_float((uint32_t)(127 + 14 - E) << 23);  // 2^(14-E): |x| * up < 2^15
+      if (lane == 0) fg[gl] = __uint_as_float((uint32_t)(127 - 14 + E) << 23);
+      int msum = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = __float2int_rn(v[i] * up);
+        msum += m;
+        const int kl = lane * 4 + i, kb = kl >> 3, r = kl & 7;
+        unsigned char* q = xq + (gl * UROWS + kb) * 16 + (r & 1) * 4 + (r >> 1);
+        q[0] = (unsigned char)((m >> 8) & 0xff);
+        q[8] = (unsigned char)(m & 0xff);
+      }
+      msum += __shfl_xor_sync(0xffffffffu, msum, 1);  // lanes 2j, 2j+1 share word row j of the group
+      if ((lane & 1) == 0) mk[gl * UROWS + (lane >> 1)] = msum;
+    }
+    consumer_sync();
+
+    const int rl = t / CQ, cq = t % CQ;
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < nunits; ++s) {
+      if (ok) ok = mbar_wait(&full[s], 0);
+      if (!ok) continue;
+      const unsigned char* wbase = stage0 + (size_t)s * STAGE;
+      int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
+      int msum = 0;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int kb = rl + RL * i;
+        const uint4 xw = *(const uint4*)(xq + (s * UROWS + kb) * 16);
+        const uint4 w4 = *(const uint4*)(wbase + kb * (TNW * 4) + cq * 16);
+        msum += mk[s * UROWS + kb];
+        const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t ne = wv[q] & 0x0F0F0F0Fu, no = (wv[q] >> 4) & 0x0F0F0F0Fu;
+          acc_h[q] = dp4a_us(ne, xw.x, acc_h[q]);
+          acc_h[q] = dp4a_us(no, xw.y, acc_h[q]);
+          acc_l[q] = dp4a_uu(ne, xw.z, acc_l[q]);
+          acc_l[q] = dp4a_uu(no, xw.w, acc_l[q]);
+        }
+      }
+      float sc[4];
+      if (p.scale_bf16) {
+        const uint2 v = *(const uint2*)(wbase + W_BYTES + cq * 8);
+        sc[0] = __uint_as_float(v.x << 16), sc[1] = __uint_as_float(v.x & 0xffff0000u);
+        sc[2] = __uint_as_float(v.y << 16), sc[3] = __uint_as_float(v.y & 0xffff0000u);
+      } else {
+        const float4 v = *(const float4*)(wbase + W_BYTES + cq * 16);
+        sc[0] = v.x, sc[1] = v.y, sc[2] = v.z, sc[3] = v.w;
+      }
+      const float f = fg[s];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int S = acc_h[q] * 256 + acc_l[q] - 8 * msum;  // sum over this thread's rows of (nibble - 8) * m
+        tot[q] = fmaf((float)S * f, sc[q], tot[q]);
+      }
+    }
+    if (!ok && lane == 0) atomicExch(a.status, 4);
+    // add the row lanes, then hand this CTA's column sums to rank 0
+    *(float4*)(red + rl * TNW + cq * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    consumer_sync();
+    if (t < TNW) {
+      float v = 0.f;
+#pragma unroll
+      for (int r = 0; r < RL; ++r) v += red[r * TNW + t];
+      if (cs == 1) {
+        const int n = tile * TNW + t;
+        if (n < p.N) epilogue_store(p, 0, n, v);
+      } else {
+        dsmem_store(dsm + rank * TNW + t, 0, v);
+      }
+    }
+  }
+  if (cs == 1) return;
+  cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
+  if (rank == 0 && t < TNW) {
+    float v = 0.f;
+    for (int r = 0; r < cs; ++r) v += dsm[r * TNW + t];
+    const int n = tile * TNW + t;
+    if (n < p.N) epilogue_store(p, 0, n, v);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return (EncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+int pick_cs(int K) {
+  const int G = K / 128;
+  return std::max(1, std::min(MAX_CS, G / 2));  // at least two groups per CTA, at most 8 CTAs per tile
+}
+
+template <int TNW>
+size_t cluster_smem(int max_units) {
+  constexpr int RL = CTHREADS / (TNW / 4);
+  const size_t stage = (size_t)UROWS * TNW * 4 + TNW * 4;
+  return (size_t)max_units * stage + (size_t)max_units * UROWS * 16 + (size_t)max_units * UROWS * 4 +
+         (size_t)((max_units + 3) & ~3) * 4 + (size_t)RL * TNW * 4 + (size_t)MAX_CS * TNW * 4 + (size_t)max_units * 8 + 32 + 128;
+}
+
+template <int TNW>
+int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) {
+    set_error("int4 gemv: cuTensorMapEncodeTiled is not available from this driver");
+    return 1;
+  }
+  CUtensorMap wmap, smap;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)(p.K / 8)};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.N * 4};
+    const cuuint32_t box[2] = {TNW, UROWS};
+    const cuuint32_t es[2] = {1, 1};
+    const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)p.packed_k8, dims, strides, box, es,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("int4 gemv (cluster): tensor map for the re-packed weight failed (code %d)", (int)r);
+      return 1;
+    }
+  }
+  {
+    const int esz = p.scale_bf16 ? 2 : 4;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)(p.K / 128)};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.N * esz};
+    const cuuint32_t box[2] = {TNW, 1};
+    const cuuint32_t es[2] = {1, 1};
+    const CUresult r = enc(&smap, p.scale_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                           (void*)p.scale, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_error("int4 gemv (cluster): tensor map for the scales failed (code %d)", (int)r);
+      return 1;
+    }
+  }
+  ClusterArgs a = {};
+  a.p = p;
+  a.cs = pick_cs(p.K);
+  const int G = p.K / 128;
+  a.max_units = (G + a.cs - 1) / a.cs;
+  a.status = status;
+  const int tiles = (p.N + TNW - 1) / TNW;
+  const size_t smem = cluster_smem<TNW>(a.max_units);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * a.cs, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = a.cs;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW>, wmap, smap, a);
+  if (e != cudaSuccess) {
+    set_error("int4 gemv (cluster): launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return check_launch("int4 gemv (cluster)");
+}
+
+}  // namespace
+
+// Shapes the cluster kernel takes: the same preconditions as the streaming kernel, N a multiple of 4
+// for 16-byte rows, and a per-CTA footprint that leaves room for several CTAs per SM.
+bool cluster_path_ok(const GemvParams& p) {
+  if (!(p.rows == 1 && p.packed_k8 != nullptr && p.group == 128 && p.K % 256 == 0 && p.N % 4 == 0 &&
+        ((uintptr_t)p.packed_k8 % 16) == 0 && ((uintptr_t)p.scale % 16) == 0 && p.math == MATH_FAST))
+    return false;
+  const int cs = pick_cs(p.K), G = p.K / 128;
+  const int max_units = (G + cs - 1) / cs;
+  const size_t smem = p.N >= 4096 ? cluster_smem<256>(max_units) : cluster_smem<128>(max_units);
+  return smem <= 100 * 1024;  // at least two CTAs per SM
+}
+
+int cluster_configure() {
+  cudaError_t e = cudaFuncSetAttribute(gemv_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
+  return 0;
+}
+
+int launch_gemv_cluster(const GemvParams& p, int* status, cudaStream_t stream) {
+  if (p.N >= 4096) return launch_cluster_tnw<256>(p, status, stream);
+  return launch_cluster_tnw<128>(p, status, stream);
+}
+
+}  // namespace dfb

@@ -24,6 +24,7 @@ struct GemvParams {
   int rows;
   // weight: packed [K/2, N] uint8 (low nibble row j, high nibble row j + K/2), scale [K/group, N]
   const uint8_t* packed;
+  const uint32_t* packed_k8;  // optional re-packed copy [K/8, N] words for the streaming kernel
   const void* scale;
   int scale_bf16;  // 0: fp32 scales, 1: bf16 scales
   int K, N, group;
@@ -46,12 +47,27 @@ struct GemvParams {
   float* partials;
   unsigned* counters;
   int math;
+  int* status;      // device word the streaming kernel sets if one of its bounded waits gives up
+  int force_tiled;  // 1: never take the streaming (TMA) path
 };
 
 // Bytes of scratch the split-K path needs for a problem, and the number of counters.
 size_t gemv_partials_bytes(int rows, int K, int N, int group);
 size_t gemv_counter_count(int rows, int K, int N, int group);
 int launch_gemv(const GemvParams& p, cudaStream_t stream);
+// streaming (TMA ring, persistent CTAs, programmatic dependent launch) variant for one activation row
+bool stream_path_ok(const GemvParams& p);
+int stream_max_slots(int K, int N);
+size_t stream_partials_bytes(int K, int N);
+size_t stream_counter_count(int K, int N);
+int stream_configure();
+// one-cluster-per-tile variant for layer-sized matrices (same re-packed weight, no global scratch)
+bool cluster_path_ok(const GemvParams& p);
+int cluster_configure();
+int launch_gemv_cluster(const GemvParams& p, int* status, cudaStream_t stream);
+int launch_gemv_stream(const GemvParams& p, int* status, cudaStream_t stream);
+// packed [K/2, N] bytes -> [K/8, N] words, word (kb, n) = the nibbles of column n, rows 8kb .. 8kb+7
+int launch_int4_repack_k8(const uint8_t* packed, int K, int N, uint32_t* out, cudaStream_t stream);
 
 int launch_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, cudaStream_t stream);
 int launch_int4_dequant(const uint8_t* packed, const void* scale, int scale_bf16, int K, int N, int group, bf16* out,

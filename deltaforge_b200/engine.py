@@ -264,7 +264,13 @@ class DecodeEngine:
         def lin(qw: QuantisedWeight) -> Linear:
             if not (qw.qweight.is_contiguous() and qw.scale.is_contiguous()):
                 raise ValueError("quantised weights must be contiguous")
-            return Linear(qw.qweight.data_ptr(), qw.scale.data_ptr(), int(qw.scale.dtype == BF16), qw.in_features, qw.out_features, qw.group_size)
+            k, n = qw.in_features, qw.out_features
+            if qw.k8 is None and self.batch == 1 and qw.group_size == 128 and k % 256 == 0 and n % 4 == 0:
+                from . import ops  # the re-packed copy the streaming GEMV reads; made once per weight
+
+                qw.k8 = ops.int4_repack_k8(qw.qweight)
+            k8 = qw.k8.data_ptr() if qw.k8 is not None else None
+            return Linear(qw.qweight.data_ptr(), qw.scale.data_ptr(), int(qw.scale.dtype == BF16), k, n, qw.group_size, k8)
 
         layers = (LayerDesc * len(weights.layers))()
         for i, (lw, cl) in enumerate(zip(weights.layers, cache.layers)):
@@ -325,6 +331,13 @@ class DecodeEngine:
     @property
     def launches_per_step(self) -> int:
         return self.lib.dfb_engine_launches_per_step(self._handle)
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a kernel gave up on one of its bounded waits."""
+        code = C.c_int(0)
+        _lib.check(self.lib.dfb_engine_status(self._handle, C.byref(code), self._stream()), "dfb_engine_status")
+        if code.value:
+            raise _lib.Dfb200Error(f"a decode kernel reported status {code.value}: a bounded wait on an asynchronous copy ran out")
 
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream

@@ -117,10 +117,18 @@ def int4_gemv_fused(
     conv_cache: Tensor | None = None,
     conv_weight: Tensor | None = None,
     math: int | None = None,
+    force_tiled: bool = False,
+    packed_k8: Tensor | None = None,
     op: str = "int4_gemv",
 ) -> Tensor:
-    """The general form behind every int4 linear op of this module. Returns ``[..., N]`` bf16."""
+    """The general form behind every int4 linear op of this module. Returns ``[..., N]`` bf16.
+
+    ``packed_k8`` is the optional re-packed copy of the weight (``int4_repack_k8``); with it, one
+    activation row and the FAST arithmetic the streaming kernel runs instead of the register-tiled one.
+    """
     k, n = _check_int4(x, packed, scale, group_size, op)
+    if packed_k8 is not None and (packed_k8.dtype != torch.int32 or tuple(packed_k8.shape) != (k // 8, n)):
+        raise ValueError(f"{op}: packed_k8 must be int32 [K/8, N] = {(k // 8, n)}, got {tuple(packed_k8.shape)} {packed_k8.dtype}")
     if prologue == PRO_RMSNORM:
         if norm_weight is None or norm_weight.shape != (k,):
             raise ValueError(f"{op}: RMSNorm weight must have {k} elements")
@@ -176,6 +184,11 @@ def int4_gemv_fused(
         d.conv_state, d.conv_w, d.conv_dim = conv_cache.data_ptr(), cw.data_ptr(), conv_dim
     d.scratch, d.scratch_bytes = _ptr(scratch), nbytes
     d.math = default_math if math is None else math
+    d.force_tiled = int(force_tiled)
+    if packed_k8 is not None:
+        packed_k8 = packed_k8.contiguous()
+        keep.append(packed_k8)
+        d.packed_k8 = packed_k8.data_ptr()
     _lib.check(lib.dfb_int4_gemv(C.byref(d), _stream(x)), f"dfb200::{op}")
     return out.reshape(*lead, n)
 
@@ -241,6 +254,26 @@ def rmsnorm_int4_gemv_conv(
 @rmsnorm_int4_gemv_conv.register_fake
 def _(x, norm_weight, eps, packed, scale, group_size, conv_cache, conv_weight):
     return x.new_empty((*x.shape[:-1], packed.shape[1]))
+
+
+@torch.library.custom_op("dfb200::int4_repack_k8", mutates_args=())
+def int4_repack_k8(packed: Tensor) -> Tensor:
+    """``packed [K/2, N]`` uint8 -> int32 ``[K/8, N]``: word ``(kb, n)`` holds the eight nibbles of column
+    ``n`` for rows ``8kb .. 8kb+7`` (nibble ``i`` = row ``8kb + i``). The layout the streaming GEMV reads."""
+    if packed.dim() != 2 or packed.dtype != torch.uint8 or (packed.shape[0] * 2) % 8:
+        raise ValueError(f"int4_repack_k8: expected uint8 [K/2, N] with K a multiple of 8, got {tuple(packed.shape)} {packed.dtype}")
+    require_cuda(packed, "int4_repack_k8")
+    packed = packed.contiguous()
+    half, n = packed.shape
+    out = torch.empty((half // 4, n), dtype=torch.int32, device=packed.device)
+    if out.numel():
+        _lib.check(_lib.load().dfb_int4_repack_k8(packed.data_ptr(), 2 * half, n, out.data_ptr(), _stream(packed)), "dfb200::int4_repack_k8")
+    return out
+
+
+@int4_repack_k8.register_fake
+def _(packed):
+    return packed.new_empty((packed.shape[0] // 4, packed.shape[1]), dtype=torch.int32)
 
 
 @torch.library.custom_op("dfb200::int4_unpack", mutates_args=())

@@ -25,6 +25,7 @@ class QuantisedWeight:
     scale: Tensor  # [K/group, N]
     bits: int
     group_size: int
+    k8: Tensor | None = None  # [K/8, N] int32: the same nibbles re-packed for the streaming GEMV (made on demand)
 
     @property
     def in_features(self) -> int:

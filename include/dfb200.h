@@ -78,10 +78,19 @@ typedef struct dfb_gemv_desc {
   void* scratch; /* dfb_int4_gemv_scratch_bytes() bytes; zero it once before first use */
   size_t scratch_bytes;
   int32_t math;
+  int32_t force_tiled; /* 1: use the register-tiled kernel even where the streaming (TMA) kernel applies */
+  const void* packed_k8; /* optional: the weight re-packed by dfb_int4_repack_k8; enables the streaming kernel */
 } dfb_gemv_desc;
 
-/* Scratch for one GEMV problem: split-K partial sums followed by one arrival counter per column tile.
- * The counters must be zero before the first launch; every launch leaves them zero again. */
+/* Re-pack a K-major int4 weight for the streaming GEMV: packed [K/2, N] bytes -> out [K/8, N] uint32,
+ * word (kb, n) = the eight nibbles (still value + 8) of column n for rows 8kb .. 8kb+7, nibble i = row
+ * 8kb + i. Same values as quantise_int4_k_major produces (src/deltaforge/kernels/tiled_gemv.py:242-278),
+ * another order; done once at install time. */
+int dfb_int4_repack_k8(const uint8_t* packed, int K, int N, void* out, void* stream);
+
+/* Scratch for one GEMV problem: split-K partial sums, one arrival counter per column tile, and in the
+ * last 256 bytes a status word (int32, 0 = ok) that the streaming kernel sets if one of its bounded
+ * waits gives up. Zero the scratch once before the first launch; every launch leaves the counters zero. */
 size_t dfb_int4_gemv_scratch_bytes(int rows, int K, int N, int group);
 
 /* y = x @ dequant(W), with optional fused prologue and epilogue. Stands in for the op
@@ -199,6 +208,7 @@ typedef struct dfb_linear {
   const void* scale;
   int32_t scale_is_bf16;
   int32_t K, N, group;
+  const void* packed_k8; /* optional re-packed copy (dfb_int4_repack_k8) */
 } dfb_linear;
 
 #define DFB_LAYER_DELTANET 0
@@ -263,6 +273,9 @@ int dfb_engine_replay(void* engine, int steps, void* stream);
  * copy the chosen token device->host and wait for it. tokens_host holds [batch] input tokens on
  * entry; out_host receives [steps, batch]. Both should be pinned for the copies to be asynchronous. */
 int dfb_engine_decode_host(void* engine, const int64_t* tokens_host, int steps, int64_t* out_host, void* stream);
+/* Wait for `stream` and read the engine's status word: 0, or the code a kernel recorded when one of its
+ * bounded waits (on a shared-memory barrier fed by asynchronous copies) gave up instead of hanging. */
+int dfb_engine_status(void* engine, int* status_host, void* stream);
 /* Number of kernel launches in one step. */
 int dfb_engine_launches_per_step(void* engine);
 
