@@ -56,6 +56,17 @@ class AttnPrepDesc(C.Structure):
     ]  # fmt: skip
 
 
+class AttnStepDesc(C.Structure):
+    _fields_ = [
+        ("batch", c_i32), ("hq", c_i32), ("hkv", c_i32), ("d", c_i32), ("rotary_dim", c_i32),
+        ("proj", c_vp), ("proj_stride", c_i64), ("q_norm_w", c_vp), ("k_norm_w", c_vp), ("eps", c_f32),
+        ("inv_freq", c_vp), ("pos", c_vp), ("kcache", c_vp), ("vcache", c_vp),
+        ("kv_batch_stride", c_i64), ("kv_head_stride", c_i64), ("max_seq", c_i32),
+        ("attn_output_gate", c_i32), ("gate_is_swish", c_i32), ("scale", c_f32), ("splits", c_i32), ("cluster_size", c_i32),
+        ("scratch", c_vp), ("scratch_bytes", c_sz), ("out", c_vp), ("out_stride", c_i64), ("status", c_vp),
+    ]  # fmt: skip
+
+
 class Linear(C.Structure):
     _fields_ = [
         ("packed", c_vp), ("scale", c_vp), ("scale_is_bf16", c_i32), ("K", c_i32), ("N", c_i32), ("group", c_i32),
@@ -104,6 +115,7 @@ SIGNATURES = {
     "dfb_attn_scratch_bytes": (c_sz, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dfb_attn_decode": (C.c_int, [C.POINTER(AttnDesc), c_vp]),
     "dfb_attn_prep": (C.c_int, [C.POINTER(AttnPrepDesc), c_vp]),
+    "dfb_attn_step": (C.c_int, [C.POINTER(AttnStepDesc), c_vp]),
     "dfb_engine_workspace_bytes": (c_sz, [C.POINTER(ModelDesc)]),
     "dfb_engine_create": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(c_vp)]),
     "dfb_engine_destroy": (C.c_int, [c_vp]),

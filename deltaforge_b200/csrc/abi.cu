@@ -246,6 +246,56 @@ int dfb_attn_decode(const dfb_attn_desc* d, void* stream) {
   return launch_attn_decode(p, (cudaStream_t)stream);
 }
 
+int dfb_attn_step(const dfb_attn_step_desc* d, void* stream) {
+  if (!d) return bad("dfb_attn_step: null descriptor");
+  if (!d->proj || !d->q_norm_w || !d->k_norm_w || !d->inv_freq || !d->pos || !d->kcache || !d->vcache || !d->out)
+    return bad("dfb_attn_step: null tensor pointer");
+  const int cs = d->cluster_size > 0 ? d->cluster_size : (d->splits < 8 ? d->splits : 8);
+  if (cs < 1 || cs > 8 || d->splits % cs) return bad("dfb_attn_step: cluster size %d does not divide %d slices", cs, d->splits);
+  if (!attn_step_ok(d->d, d->hq, d->hkv, d->rotary_dim, d->splits, d->max_seq))
+    return bad("dfb_attn_step: unsupported shape (d=%d, hq=%d, hkv=%d, rotary=%d, splits=%d, max_seq=%d)", d->d, d->hq, d->hkv,
+               d->rotary_dim, d->splits, d->max_seq);
+  const size_t need = dfb_attn_scratch_bytes(d->batch, d->hq, d->hkv, d->d, d->splits);
+  if (need && (!d->scratch || d->scratch_bytes < need)) return bad("dfb_attn_step: scratch of %zu bytes required", need);
+  AttnStepParams p = {};
+  p.batch = d->batch;
+  p.hq = d->hq;
+  p.hkv = d->hkv;
+  p.d = d->d;
+  p.rotary_dim = d->rotary_dim;
+  p.proj = (const bf16*)d->proj;
+  p.proj_stride = d->proj_stride;
+  p.q_norm_w = (const bf16*)d->q_norm_w;
+  p.k_norm_w = (const bf16*)d->k_norm_w;
+  p.eps = d->eps;
+  p.inv_freq = d->inv_freq;
+  p.pos = d->pos;
+  p.kcache = (bf16*)d->kcache;
+  p.vcache = (bf16*)d->vcache;
+  p.kv_batch_stride = d->kv_batch_stride;
+  p.kv_head_stride = d->kv_head_stride;
+  p.max_seq = d->max_seq;
+  p.attn_output_gate = d->attn_output_gate;
+  p.gate_swish = d->gate_is_swish;
+  p.scale = d->scale;
+  p.splits = d->splits;
+  p.cluster_size = cs;
+  if (need) {
+    char* s = (char*)d->scratch;
+    p.part_acc = (float*)s;
+    s += align_up((size_t)d->batch * d->hq * d->splits * d->d * 4, 256);
+    p.part_ml = (float*)s;
+    s += align_up((size_t)d->batch * d->hq * d->splits * 2 * 4, 256);
+    p.counters = (unsigned*)s;
+  }
+  p.out = (bf16*)d->out;
+  p.out_stride = d->out_stride;
+  p.status = d->status;
+  static const int configured = attn_step_configure();
+  if (configured) return configured;
+  return launch_attn_step(p, (cudaStream_t)stream);
+}
+
 int dfb_attn_prep(const dfb_attn_prep_desc* d, void* stream) {
   if (!d) return bad("dfb_attn_prep: null descriptor");
   if (!d->proj || !d->q_norm_w || !d->k_norm_w || !d->inv_freq || !d->pos || !d->q_out || !d->kcache || !d->vcache)

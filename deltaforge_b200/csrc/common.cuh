@@ -68,6 +68,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 
+// Ask for the largest shared-memory carve-out for a kernel. Every kernel of the decode step does,
+// including those that use almost none: if consecutive kernels asked for different L1/shared splits
+// the SMs would have to drain and re-partition between them.
+template <typename K>
+inline cudaError_t prefer_max_shared(K kernel) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 // Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait()
 // before it reads or writes anything an earlier kernel of the stream touches).
 template <typename... KArgs, typename... Args>

@@ -21,9 +21,14 @@ namespace dfb {
 
 int gemv_configure();
 int attn_configure();
+int deltanet_configure();
+int elementwise_configure();
 
 int configure_kernels() {
   if (int rc = gemv_configure()) return rc;
+  if (int rc = attn_step_configure()) return rc;
+  if (int rc = deltanet_configure()) return rc;
+  if (int rc = elementwise_configure()) return rc;
   return attn_configure();
 }
 
@@ -173,6 +178,53 @@ struct Engine {
         if (rc) return rc;
         const int d_ = m.head_dim;
         const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
+        if (attn_step_ok(d_, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) {
+          // norms, RoPE, KV write, split-KV decode, merge and gate in one launch
+          AttnStepParams q = {};
+          q.batch = m.batch;
+          q.hq = m.hq;
+          q.hkv = m.hkv;
+          q.d = d_;
+          q.rotary_dim = m.rotary_dim;
+          q.proj = proj;
+          q.proj_stride = pstride;
+          q.q_norm_w = (const bf16*)L.q_norm_w;
+          q.k_norm_w = (const bf16*)L.k_norm_w;
+          q.eps = m.eps;
+          q.inv_freq = m.inv_freq;
+          q.pos = m.pos;
+          q.kcache = (bf16*)L.kcache;
+          q.vcache = (bf16*)L.vcache;
+          q.kv_batch_stride = kvb;
+          q.kv_head_stride = kvh;
+          q.max_seq = m.max_seq;
+          q.attn_output_gate = m.attn_output_gate;
+          q.gate_swish = m.gate_is_swish;
+          q.scale = 1.0f / sqrtf((float)d_);
+          q.splits = m.attn_splits;
+          q.cluster_size = std::min(m.attn_splits, 8);
+          if (m.attn_splits > 1) {
+            char* sc = at(ws.attn);
+            q.part_acc = (float*)sc;
+            sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
+            q.part_ml = (float*)sc;
+            sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
+            q.counters = (unsigned*)sc;
+          }
+          q.out = mix;
+          q.out_stride = (long)m.hq * d_;
+          q.status = (int*)at(ws.status);
+          rc = launch_attn_step(q, s);
+          ++launches;
+          if (rc) return rc;
+          rc = gemv(L.out_proj, mix, (long)m.hq * d_, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+          if (rc) return rc;
+          rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
+          if (rc) return rc;
+          rc = gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
+          if (rc) return rc;
+          continue;
+        }
         AttnPrepParams pp = {};
         pp.batch = m.batch;
         pp.hq = m.hq;

@@ -191,6 +191,12 @@ __global__ void __launch_bounds__(DN_WARPS * 32) delta_rule_kernel(const DeltaRu
 
 }  // namespace
 
+int deltanet_configure() {
+  cudaError_t e = prefer_max_shared(deltanet_fused_kernel);
+  if (e == cudaSuccess) e = prefer_max_shared(delta_rule_kernel);
+  return e == cudaSuccess ? 0 : check_launch("deltanet step: shared-memory carve-out");
+}
+
 int launch_deltanet_step(const DeltaNetParams& p, cudaStream_t stream) {
   if (p.batch <= 0) return 0;
   if (p.dk > MAX_DK || p.dv > 8 * VB || p.dk < 1 || p.dv < 1) {

@@ -201,6 +201,13 @@ int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch
   return check_launch("causal_conv_step");
 }
 
+int elementwise_configure() {
+  cudaError_t e = prefer_max_shared(embed_kernel);
+  if (e == cudaSuccess) e = prefer_max_shared(argmax_kernel);
+  if (e == cudaSuccess) e = prefer_max_shared(advance_kernel);
+  return e == cudaSuccess ? 0 : check_launch("elementwise: shared-memory carve-out");
+}
+
 int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s) {
   if (batch <= 0) return 0;
   if (launch_pdl(embed_kernel, dim3(batch), dim3(128), 0, s, table, tokens, hidden, out) != cudaSuccess) return check_launch("embed");

@@ -372,6 +372,8 @@ bool cluster_path_ok(const GemvParams& p) {
 int cluster_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemv_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (e == cudaSuccess) e = prefer_max_shared(gemv_cluster_kernel<256>);
+  if (e == cudaSuccess) e = prefer_max_shared(gemv_cluster_kernel<128>);
   if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
   return 0;
 }

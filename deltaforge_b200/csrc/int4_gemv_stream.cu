@@ -467,6 +467,8 @@ size_t stream_counter_count(int K, int N) {
 int stream_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e == cudaSuccess) e = prefer_max_shared(gemv_stream_kernel<4>);
+  if (e == cudaSuccess) e = prefer_max_shared(gemv_stream_kernel<2>);
   if (e != cudaSuccess) return check_launch("int4 gemv (stream): shared-memory opt-in");
   if (!encode_fn()) {
     set_error("int4 gemv (stream): cuTensorMapEncodeTiled is not available from this driver");

@@ -148,6 +148,34 @@ struct AttnPrepParams {  // q/k RMSNorm + partial RoPE + KV-cache write for the 
 };
 int launch_attn_prep(const AttnPrepParams& p, cudaStream_t stream);
 
+struct AttnStepParams {  // prep + split-KV decode + merge + gate in one launch (head_dim 256)
+  int batch, hq, hkv, d, rotary_dim;
+  const bf16* proj;  // [batch, hq*(2d or d) + 2*hkv*d]: per head query(|gate), then keys, then values
+  long proj_stride;
+  const bf16* q_norm_w;
+  const bf16* k_norm_w;
+  float eps;
+  const float* inv_freq;
+  const int* pos;  // device scalar: tokens already cached; the new token goes to row *pos
+  bf16* kcache;
+  bf16* vcache;
+  long kv_batch_stride, kv_head_stride;
+  int max_seq;
+  int attn_output_gate, gate_swish;
+  float scale;
+  int splits;        // power of two, grid.x
+  int cluster_size;  // min(splits, 8)
+  float* part_acc;   // [batch, hq, splits / cluster_size, d]
+  float* part_ml;    // [batch, hq, splits / cluster_size, 2]
+  unsigned* counters;  // [batch * hkv]
+  bf16* out;  // [batch, hq*d]
+  long out_stride;
+  int* status;  // device word set if the bounded wait on the staging copies gives up
+};
+bool attn_step_ok(int d, int hq, int hkv, int rotary_dim, int splits, int max_seq);
+int attn_step_configure();
+int launch_attn_step(const AttnStepParams& p, cudaStream_t stream);
+
 int launch_rms_norm(const bf16* x, const bf16* w, float eps, int rows, int n, bf16* out, cudaStream_t s);
 int launch_add_rms_norm(const bf16* x, const bf16* res, const bf16* w, float eps, int rows, int n, bf16* resid_out,
                         bf16* out, cudaStream_t s);

@@ -233,6 +233,16 @@ class DecodeCache:
 def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: int = 148) -> int:
     """Enough key slices that batch * kv_heads * splits CTAs cover the SMs about twice, with at least
     64 keys per slice; a power of two between 1 and 64."""
+    # The fused attention kernel stages a slice of at most 160 keys in shared memory, one CTA per SM,
+    # and its cost grows with the number of CTAs: take the fewest slices that fit (up to 128).
+    splits = 1
+    while splits < 128 and -(-max_seq_len // splits) > 160:
+        splits *= 2
+    if -(-max_seq_len // splits) <= 160:
+        while splits * 2 * batch * kv_heads <= sm_count and max_seq_len // (splits * 2) >= 64:
+            splits *= 2  # short caches: still use the SMs
+        return splits
+    # longer caches take the two-kernel path, which has no slice limit
     want = max(1, (2 * sm_count) // max(1, batch * kv_heads))
     splits = 1
     while splits * 2 <= min(want, 64) and max_seq_len // (splits * 2) >= 64:

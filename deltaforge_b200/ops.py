@@ -703,3 +703,60 @@ def attn_prep(
 @attn_prep.register_fake
 def _(proj, q_norm_weight, k_norm_weight, eps, inv_freq, pos, key_cache, value_cache, num_heads, output_gate):
     return proj.new_empty((proj.shape[0], num_heads, key_cache.shape[3]))
+
+
+@torch.library.custom_op("dfb200::attn_step", mutates_args=("key_cache", "value_cache"))
+def attn_step(
+    proj: Tensor, q_norm_weight: Tensor, k_norm_weight: Tensor, eps: float, inv_freq: Tensor, pos: Tensor,
+    key_cache: Tensor, value_cache: Tensor, num_heads: int, output_gate: bool, swish: bool, splits: int, cluster_size: int,
+) -> Tensor:  # fmt: skip
+    """``attn_prep`` + gated split-KV decode attention in one launch, for one new token per sequence.
+
+    ``proj (B, width)`` is the fused ``q(|gate)|k|v`` projection row, ``pos`` the device-side number of
+    cached tokens (the new token becomes row ``pos`` of the caches). Returns ``(B, Hq * D)`` bf16.
+    ``splits`` is a power of two with ``ceil(max_seq / splits) <= 160``; ``cluster_size`` 0 picks min(splits, 8).
+    """
+    if key_cache.dim() != 4 or key_cache.shape != value_cache.shape:
+        raise ValueError(f"caches must both be (batch, kv_heads, max_seq, head_dim), got {tuple(key_cache.shape)}")
+    batch, hkv, max_seq, d = key_cache.shape
+    width = num_heads * d * (2 if output_gate else 1) + 2 * hkv * d
+    if proj.shape != (batch, width):
+        raise ValueError(f"proj must be {(batch, width)}, got {tuple(proj.shape)}")
+    if q_norm_weight.shape != (d,) or k_norm_weight.shape != (d,):
+        raise ValueError(f"q/k norm weights must have {d} elements")
+    if splits < 1 or splits & (splits - 1):
+        raise ValueError(f"splits must be a power of two, got {splits}")
+    if -(-max_seq // splits) > 160:
+        raise ValueError(f"{splits} slices of a {max_seq}-row cache exceed 160 keys per slice")
+    if pos.dtype != torch.int32 or pos.numel() != 1:
+        raise ValueError("pos must be a single int32 on the device")
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("the KV caches are written in place and must be contiguous")
+    if proj.dtype != BF16 or key_cache.dtype != BF16:
+        raise ValueError("attn_step: activations and caches must be bfloat16")
+    require_cuda(proj, "attn_step")
+    proj = proj.contiguous()
+    qw, kw = q_norm_weight.to(BF16).contiguous(), k_norm_weight.to(BF16).contiguous()
+    inv = inv_freq.float().contiguous()
+    out = torch.empty((batch, num_heads * d), device=proj.device, dtype=BF16)
+    lib = _lib.load()
+    nbytes = lib.dfb_attn_scratch_bytes(batch, num_heads, hkv, d, splits)
+    scratch = _zeroed_scratch(proj.device, ("attn", batch, num_heads, hkv, d, splits), nbytes)
+    a = _lib.AttnStepDesc()
+    a.batch, a.hq, a.hkv, a.d, a.rotary_dim = batch, num_heads, hkv, d, 2 * inv.numel()
+    a.proj, a.proj_stride = proj.data_ptr(), width
+    a.q_norm_w, a.k_norm_w, a.eps = qw.data_ptr(), kw.data_ptr(), eps
+    a.inv_freq, a.pos = inv.data_ptr(), pos.data_ptr()
+    a.kcache, a.vcache = key_cache.data_ptr(), value_cache.data_ptr()
+    a.kv_batch_stride, a.kv_head_stride, a.max_seq = hkv * max_seq * d, max_seq * d, max_seq
+    a.attn_output_gate, a.gate_is_swish, a.scale = int(output_gate), int(swish), d**-0.5
+    a.splits, a.cluster_size = splits, cluster_size
+    a.scratch, a.scratch_bytes = _ptr(scratch), nbytes
+    a.out, a.out_stride, a.status = out.data_ptr(), num_heads * d, None
+    _lib.check(lib.dfb_attn_step(C.byref(a), _stream(proj)), "dfb200::attn_step")
+    return out
+
+
+@attn_step.register_fake
+def _(proj, q_norm_weight, k_norm_weight, eps, inv_freq, pos, key_cache, value_cache, num_heads, output_gate, swish, splits, cluster_size):
+    return proj.new_empty((proj.shape[0], num_heads * key_cache.shape[3]))

@@ -201,6 +201,35 @@ typedef struct dfb_attn_prep_desc {
  * src/deltaforge/reference.py:632-650. */
 int dfb_attn_prep(const dfb_attn_prep_desc* desc, void* stream);
 
+typedef struct dfb_attn_step_desc {
+  int32_t batch, hq, hkv, d, rotary_dim;
+  const void* proj; /* bf16 [batch, hq*(2d or d) + 2*hkv*d]: per head query(|gate), then keys, then values */
+  int64_t proj_stride;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  float eps;
+  const float* inv_freq;
+  const int32_t* pos; /* device scalar: tokens already cached; the new token is row *pos */
+  void* kcache;       /* bf16 [batch, hkv, max_seq, d] */
+  void* vcache;
+  int64_t kv_batch_stride, kv_head_stride;
+  int32_t max_seq;
+  int32_t attn_output_gate, gate_is_swish;
+  float scale;
+  int32_t splits;       /* power of two; ceil(max_seq / splits) <= 160 */
+  int32_t cluster_size; /* 0 = min(splits, 8) */
+  void* scratch;        /* dfb_attn_scratch_bytes(batch, hq, hkv, d, splits); zero once */
+  size_t scratch_bytes;
+  void* out; /* bf16 [batch, hq*d] */
+  int64_t out_stride;
+  int32_t* status; /* optional device word, set non-zero if the bounded wait on the staging copies gives up */
+} dfb_attn_step_desc;
+
+/* dfb_attn_prep followed by dfb_attn_decode with the output gate, in one launch: everything of
+ * GatedAttention.forward between q/k/v_proj and o_proj for one new token (src/deltaforge/reference.py:
+ * 621-676). Takes head_dim 256 and 1, 2 or 4 query heads per KV head. */
+int dfb_attn_step(const dfb_attn_step_desc* desc, void* stream);
+
 /* ---- whole decode step ------------------------------------------------------------------------- */
 
 typedef struct dfb_linear {
