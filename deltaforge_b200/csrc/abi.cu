@@ -250,7 +250,7 @@ int dfb_attn_step(const dfb_attn_step_desc* d, void* stream) {
   if (!d) return bad("dfb_attn_step: null descriptor");
   if (!d->proj || !d->q_norm_w || !d->k_norm_w || !d->inv_freq || !d->pos || !d->kcache || !d->vcache || !d->out)
     return bad("dfb_attn_step: null tensor pointer");
-  const int cs = d->cluster_size > 0 ? d->cluster_size : (d->splits < 8 ? d->splits : 8);
+  const int cs = d->cluster_size > 0 ? d->cluster_size : (d->splits < 4 ? d->splits : 4);
   if (cs < 1 || cs > 8 || d->splits % cs) return bad("dfb_attn_step: cluster size %d does not divide %d slices", cs, d->splits);
   if (!attn_step_ok(d->d, d->hq, d->hkv, d->rotary_dim, d->splits, d->max_seq))
     return bad("dfb_attn_step: unsupported shape (d=%d, hq=%d, hkv=%d, rotary=%d, splits=%d, max_seq=%d)", d->d, d->hq, d->hkv,

@@ -92,6 +92,7 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 __device__ __noinline__ void norm_rope_row(const bf16* src, const bf16* nw, float eps, const float* inv_freq, int rd, int pos,
                                            float* row) {
   const int lane = threadIdx.x & 31;
+  const float f0 = lane < rd / 2 ? inv_freq[lane] : 0.f;  // in flight with the row itself
   float x[8], w[8];
   unpack8(*(const uint4*)(src + lane * 8), x);
   unpack8(*(const uint4*)(nw + lane * 8), w);
@@ -109,7 +110,7 @@ __device__ __noinline__ void norm_rope_row(const bf16* src, const bf16* nw, floa
 #pragma unroll 1
   for (int d = lane; d < half; d += 32) {
     const float a = row[d], bb = row[d + half];
-    const float ang = __fmul_rn((float)pos, inv_freq[d]);
+    const float ang = __fmul_rn((float)pos, d == lane ? f0 : inv_freq[d]);
     float s, c;
     sincosf(ang, &s, &c);
     c = round_bf16(c), s = round_bf16(s);
@@ -186,6 +187,10 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     if (pos < p.max_seq)
       *(uint4*)(p.vcache + (long)b * p.kv_batch_stride + (long)hk * p.kv_head_stride + (long)pos * D + lane * 8) = raw;
   }
+  // the output-gate logits are needed last: fetch them now
+  float gate_v[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) gate_v[g] = p.attn_output_gate ? bf2f(proj[(long)(hk * GROUPS + g) * qw + D + t]) : 0.f;
   bool ok = true;
   if (n_old > 0) ok = mbar_wait(bar, 0);
   if (!ok && t == 0 && p.status) atomicExch(p.status, 5);
@@ -204,22 +209,32 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
   }
+  // two keys per iteration: their score reductions and exponentials interleave
 #pragma unroll 1
-  for (int j = warp; j < n_keys; j += AW) {
-    float kf[8], vf[8];
+  for (int j = warp; j < n_keys; j += 2 * AW) {
+    const bool two = (j + AW) < n_keys;
+    const int j2 = two ? j + AW : j;
+    float kf[8], vf[8], kf2[8], vf2[8];
     unpack8(*(const uint4*)(kst + j * D + lane * 8), kf);
     unpack8(*(const uint4*)(vst + j * D + lane * 8), vf);
+    unpack8(*(const uint4*)(kst + j2 * D + lane * 8), kf2);
+    unpack8(*(const uint4*)(vst + j2 * D + lane * 8), vf2);
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
-      float s = 0.f;
+      float s = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s = fmaf(qr[g][i], kf[i], s);
+      for (int i = 0; i < 8; ++i) {
+        s = fmaf(qr[g][i], kf[i], s);
+        s2 = fmaf(qr[g][i], kf2[i], s2);
+      }
       s = warp_sum(s);
-      const float mn = fmaxf(m[g], s);
-      const float corr = __expf(m[g] - mn), pe = __expf(s - mn);
-      l[g] = l[g] * corr + pe;
+      s2 = warp_sum(s2);
+      if (!two) s2 = -INFINITY;
+      const float mn = fmaxf(m[g], fmaxf(s, s2));
+      const float corr = __expf(m[g] - mn), pe = __expf(s - mn), pe2 = __expf(s2 - mn);
+      l[g] = l[g] * corr + pe + pe2;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * corr + pe * vf[i];
+      for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * corr + pe * vf[i] + pe2 * vf2[i];
       m[g] = mn;
     }
   }
@@ -316,13 +331,20 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     __syncthreads();
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
+      // all of a head's cluster partials in flight together, then the weighted sum
       const long ph = ((long)b * p.hq + hq0 + g) * nclusters;
+      float pa[16], pl[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        pa[c] = c < nclusters ? __ldcg(&p.part_acc[(ph + c) * D + t]) : 0.f;
+        pl[c] = c < nclusters ? __ldcg(&p.part_ml[(ph + c) * 2 + 1]) : 0.f;
+      }
       float og = 0.f, lg = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < nclusters; ++c) {
-        const float w = wgt[g * 16 + c];
-        og = fmaf(w, __ldcg(&p.part_acc[(ph + c) * D + t]), og);
-        lg = fmaf(w, __ldcg(&p.part_ml[(ph + c) * 2 + 1]), lg);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float w = c < nclusters ? wgt[g * 16 + c] : 0.f;
+        og = fmaf(w, pa[c], og);
+        lg = fmaf(w, pl[c], lg);
       }
       o[g] = og, lt[g] = lg;
     }
@@ -333,7 +355,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   for (int g = 0; g < GROUPS; ++g) {
     float y = round_bf16(o[g] / lt[g]);
     if (p.attn_output_gate) {
-      const float gv = bf2f(proj[(long)(hq0 + g) * qw + D + t]);
+      const float gv = gate_v[g];
       const float gg = round_bf16(p.gate_swish ? silu_f(gv) : sigmoid_f(gv));
       y = round_bf16(__fmul_rn(y, gg));
     }

@@ -202,7 +202,7 @@ struct Engine {
           q.gate_swish = m.gate_is_swish;
           q.scale = 1.0f / sqrtf((float)d_);
           q.splits = m.attn_splits;
-          q.cluster_size = std::min(m.attn_splits, 8);
+          q.cluster_size = std::min(m.attn_splits, 4);  // these CTAs fill an SM each: small clusters schedule sooner
           if (m.attn_splits > 1) {
             char* sc = at(ws.attn);
             q.part_acc = (float*)sc;

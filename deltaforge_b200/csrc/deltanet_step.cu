@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   __shared__ float red[2 * DN_WARPS * VB];
   __shared__ float wred[DN_WARPS];
   __shared__ float gates[2];
-  __shared__ float cluster_ss;
+  __shared__ float cluster_ss[8];  // sums of squares of the head's column blocks, one slot per cluster rank
 
   cg::cluster_group cluster = cg::this_cluster();
   const int nvb = (p.dv + VB - 1) / VB;  // == cluster size
@@ -139,14 +139,15 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
 
   // 4. Gated RMSNorm over the head's dv outputs: the CTAs of the cluster swap their sums of squares.
   const float ob = col_ok ? round_bf16(o) : 0.f;
+  // Each CTA pushes its sum into slot [its rank] of every CTA of the cluster, so that after one
+  // cluster barrier everybody reads only its own shared memory and may leave at once.
   if (warp == 0) {
     const float ss = warp_sum(ob * ob);
-    if (lane == 0) cluster_ss = ss;
+    if (lane < nvb) *cluster.map_shared_rank(&cluster_ss[vb], lane) = ss;
   }
   cluster.sync();
   float tot = 0.f;
-  for (int rk = 0; rk < nvb; ++rk) tot += *cluster.map_shared_rank(&cluster_ss, rk);
-  cluster.sync();  // nobody leaves (and frees its shared memory) while a peer may still read it
+  for (int rk = 0; rk < nvb; ++rk) tot += cluster_ss[rk];
   if (warp == 0 && col_ok) {
     const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)dv), p.eps));
     const float nrm = round_bf16(__fmul_rn(ob, rstd));

@@ -25,6 +25,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemv_common.cuh"
 
@@ -279,6 +280,8 @@ EncodeTiledFn encode_fn() {
 
 int pick_cs(int K) {
   const int G = K / 128;
+  static const int env_cs = getenv("DFB_CLUSTER_CS") ? atoi(getenv("DFB_CLUSTER_CS")) : 0;
+  if (env_cs > 0) return std::max(1, std::min(std::min(MAX_CS, env_cs), G));
   return std::max(1, std::min(MAX_CS, G / 2));  // at least two groups per CTA, at most 8 CTAs per tile
 }
 

@@ -714,7 +714,7 @@ def attn_step(
 
     ``proj (B, width)`` is the fused ``q(|gate)|k|v`` projection row, ``pos`` the device-side number of
     cached tokens (the new token becomes row ``pos`` of the caches). Returns ``(B, Hq * D)`` bf16.
-    ``splits`` is a power of two with ``ceil(max_seq / splits) <= 160``; ``cluster_size`` 0 picks min(splits, 8).
+    ``splits`` is a power of two with ``ceil(max_seq / splits) <= 160``; ``cluster_size`` 0 picks min(splits, 4).
     """
     if key_cache.dim() != 4 or key_cache.shape != value_cache.shape:
         raise ValueError(f"caches must both be (batch, kv_heads, max_seq, head_dim), got {tuple(key_cache.shape)}")

@@ -217,7 +217,7 @@ typedef struct dfb_attn_step_desc {
   int32_t attn_output_gate, gate_is_swish;
   float scale;
   int32_t splits;       /* power of two; ceil(max_seq / splits) <= 160 */
-  int32_t cluster_size; /* 0 = min(splits, 8) */
+  int32_t cluster_size; /* 1..8 dividing splits, with splits / cluster_size <= 16; 0 = min(splits, 4) */
   void* scratch;        /* dfb_attn_scratch_bytes(batch, hq, hkv, d, splits); zero once */
   size_t scratch_bytes;
   void* out; /* bf16 [batch, hq*d] */
