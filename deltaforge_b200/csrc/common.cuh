@@ -58,15 +58,16 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void* p, uint64_t pol) {
   return r;
 }
 
-// Programmatic dependent launch: a kernel that opens with pdl_prologue() lets its successor in the
-// stream start early and then waits until everything its predecessors wrote is visible. Without the
-// launch attribute both instructions do nothing.
+// Programmatic dependent launch: pdl_launch_dependents() lets the next kernel of the stream start its
+// own prologue early; pdl_wait() blocks until everything the preceding kernels wrote is visible.
+// Without the launch attribute both instructions do nothing.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Error reporting shared by the C entry points (defined in abi.cu).
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
+int check_int4_shape(int K, int N, int group);  // 0, or DFB_ERR_ARG with the message set
 
 // Ask for the largest shared-memory carve-out for a kernel. Every kernel of the decode step does,
 // including those that use almost none: if consecutive kernels asked for different L1/shared splits

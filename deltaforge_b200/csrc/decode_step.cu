@@ -37,7 +37,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -79,6 +79,7 @@ Workspace plan(const dfb_model_desc& m) {
   w.am_idx = take(B * 64 * 4);
   w.am_ctr = take(B * 4);
   w.status = take(256);
+  w.h_ss = take(256 * 4);
   w.total = off;
   return w;
 }
@@ -90,11 +91,13 @@ struct Engine {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   int launches = 0;
+  bool ss_valid = false;  // the residual stream's per-tile sums of squares in h_ss are current
 
   char* at(size_t off) const { return (char*)m.workspace + off; }
 
   int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
            long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
+    const bool x_is_h = (const void*)x == (const void*)at(ws.h);
     GemvParams p = {};
     p.x = x;
     p.x_stride = x_stride;
@@ -125,6 +128,16 @@ struct Engine {
     p.counters = (unsigned*)at(ws.counters);
     p.math = m.math;
     p.status = (int*)at(ws.status);
+    // Sum-of-squares hand-off along the residual stream (batch 1, cluster kernel on both sides).
+    const int h_tiles = (m.hidden + cluster_tile_width(m.hidden) - 1) / cluster_tile_width(m.hidden);
+    if (prologue == PRO_RMSNORM && x_is_h && ss_valid) {
+      p.ss_in = (const float*)at(ws.h_ss);
+      p.ss_count = h_tiles;
+    }
+    if (epilogue == EPI_RESIDUAL) {
+      ss_valid = m.batch == 1 && h_tiles <= 256 && l.N < 65536 && cluster_path_ok(p);
+      if (ss_valid) p.ss_out = (float*)at(ws.h_ss);
+    }
     ++launches;
     return launch_gemv(p, s);
   }
@@ -137,7 +150,9 @@ struct Engine {
     bf16* qout = (bf16*)at(ws.qout);
     bf16* gu = (bf16*)at(ws.gu);
     const int H = m.hidden, I = m.intermediate;
-    int rc = launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, h, s);
+    const int h_tiles = (H + cluster_tile_width(H) - 1) / cluster_tile_width(H);
+    ss_valid = m.batch == 1 && h_tiles <= 256;
+    int rc = launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, h, ss_valid ? (float*)at(ws.h_ss) : nullptr, h_tiles, s);
     ++launches;
     if (rc) return rc;
     for (int i = 0; i < m.num_layers; ++i) {

@@ -85,15 +85,26 @@ __global__ void causal_conv_step_kernel(const bf16* x, bf16* cache, const bf16* 
 }
 
 // Row gather of the embedding table (src/deltaforge/reference.py:804).
-__global__ void embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out) {
+__global__ void __launch_bounds__(128) embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out, float* ss_out,
+                                                    int ss_count) {
+  __shared__ float wred[4];
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x;
   const int64_t tok = tokens[b];
-  const uint4* src = (const uint4*)(table + tok * hidden);
-  uint4* dst = (uint4*)(out + (long)b * hidden);
-  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
-  for (int i = (hidden / 8) * 8 + threadIdx.x; i < hidden; i += blockDim.x) out[(long)b * hidden + i] = table[tok * hidden + i];
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const bf16 v = table[tok * hidden + i];
+    out[(long)b * hidden + i] = v;
+    ss = fmaf(bf2f(v), bf2f(v), ss);
+  }
+  if (ss_out == nullptr || b != 0) return;
+  // sum of squares of the row, in the form the RMSNorm-prologue GEMV after this kernel reads it
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) ss_out[0] = (wred[0] + wred[1]) + (wred[2] + wred[3]);
+  for (int i = 1 + threadIdx.x; i < ss_count; i += blockDim.x) ss_out[i] = 0.f;
 }
 
 // argmax over a row of logits, first index on ties (what torch.argmax returns on the reference's CPU
@@ -208,9 +219,11 @@ int elementwise_configure() {
   return e == cudaSuccess ? 0 : check_launch("elementwise: shared-memory carve-out");
 }
 
-int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s) {
+int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, float* ss_out, int ss_count,
+                 cudaStream_t s) {
   if (batch <= 0) return 0;
-  if (launch_pdl(embed_kernel, dim3(batch), dim3(128), 0, s, table, tokens, hidden, out) != cudaSuccess) return check_launch("embed");
+  if (launch_pdl(embed_kernel, dim3(batch), dim3(128), 0, s, table, tokens, hidden, out, ss_out, ss_count) != cudaSuccess)
+    return check_launch("embed");
   return check_launch("embed");
 }
 

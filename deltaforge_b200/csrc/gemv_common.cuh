@@ -40,13 +40,14 @@ __device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
   return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
 }
 
-// Output element (r, n) from its fp32 sum.
-__device__ __forceinline__ void epilogue_store(const GemvParams& p, int r, int n, float sum) {
+// Output element (r, n) from its fp32 sum; returns the value stored (as fp32).
+__device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int n, float sum) {
   bf16 y = f2bf(sum);
   if (p.epilogue == EPI_RESIDUAL) {
     float h = bf2f(p.residual[(long)r * p.res_stride + n]);
-    p.out[(long)r * p.out_stride + n] = f2bf(__fadd_rn(h, bf2f(y)));
-    return;
+    const bf16 o = f2bf(__fadd_rn(h, bf2f(y)));
+    p.out[(long)r * p.out_stride + n] = o;
+    return bf2f(o);
   }
   if (p.epilogue == EPI_CONV && n < p.conv_dim) {
     // 4-tap depthwise causal conv decode step (src/deltaforge/kernels/inline_causal_conv.py:111-129):
@@ -59,13 +60,15 @@ __device__ __forceinline__ void epilogue_store(const GemvParams& p, int r, int n
     acc = __fadd_rn(acc, __fmul_rn(h2, bf2f(w[2])));
     acc = __fadd_rn(acc, __fmul_rn(xv, bf2f(w[3])));
     float a = round_bf16(acc);
-    p.out[(long)r * p.out_stride + n] = f2bf(silu_f(a));
+    const bf16 o = f2bf(silu_f(a));
+    p.out[(long)r * p.out_stride + n] = o;
     st[0] = st[1];
     st[1] = st[2];
     st[2] = y;
-    return;
+    return bf2f(o);
   }
   p.out[(long)r * p.out_stride + n] = y;
+  return bf2f(y);
 }
 
 }  // namespace dfb

