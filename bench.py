@@ -45,6 +45,9 @@ WORKLOAD = "qwen3.5-4b int4 decode step, batch 1, ctx 4096 (BASELINE configs[2])
 METRIC = "decode tokens/s (bs1, 4K ctx)"
 
 
+HEAD_GEMV_DRAM_BYTES_PER_LAUNCH = 327_891_968 + 4_020_096  # read + write, mean of two captured launches
+
+
 def measured_peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -235,13 +238,21 @@ def time_head_gemv(weights, iters: int = 30) -> tuple[float, int]:
     for _ in range(5):
         call()
     torch.cuda.synchronize()
+    # `iters` launches recorded into one CUDA graph, so that the host's per-call cost is outside the timed region
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            call()
+    graph.replay()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 4
     e0.record()
-    for _ in range(iters):
-        call()
+    for _ in range(reps):
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters, gemv_bytes(k, n, rows=1, scale_bytes=head.scale.element_size())
+    return e0.elapsed_time(e1) / (iters * reps), gemv_bytes(k, n, rows=1, scale_bytes=head.scale.element_size())
 
 
 def run_ours(args) -> dict | None:
@@ -254,7 +265,7 @@ def run_ours(args) -> dict | None:
     dist, rank, world, local = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    cfg = qwen3_5_4b_config()
+    cfg = qwen3_5_4b_config() if args.layers is None else qwen3_5_4b_config(num_hidden_layers=args.layers)
     steps, warmup = args.steps, max(args.warmup, 3)
     weights = synth.random_model_weights(cfg, seed=1234 + rank, device=dev, scale_dtype=torch.bfloat16)
     cache = E.DecodeCache(cfg, BATCH, CONTEXT + steps + warmup + 8, device=dev)
@@ -329,7 +340,7 @@ def run_ours(args) -> dict | None:
         "dtype": "int4 weights, bf16 activations, fp32 accumulate and recurrent state",
         "data": "synthetic",
         "config": {
-            "workload": WORKLOAD,
+            "workload": WORKLOAD if args.layers is None else f"{WORKLOAD} CUT TO {args.layers} LAYERS (profiler captures only, not a bench value)",
             "batch_per_gpu": BATCH,
             "context": CONTEXT,
             "sequences": world * BATCH,
@@ -358,7 +369,9 @@ def run_ours(args) -> dict | None:
             "peak_kind": f"of {peak_kind}",
             "bytes_per_launch": head_bytes,
             "us_per_launch": head_ms * 1e3,
-            "traffic": None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this matrix, from the ncu
+            # capture summarised in profiles/gemv_stream_kernel_lm_head.md (not re-measured by this run)
+            "traffic": HEAD_GEMV_DRAM_BYTES_PER_LAUNCH,
         },
         "roofline_step": {
             "bound": "hbm",
@@ -382,6 +395,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU port leg of the default run")
+    ap.add_argument(
+        "--layers",
+        type=int,
+        default=None,
+        help="cut the model to this many layers (a multiple of 4) so that a profiler capture holds little device memory; "
+        "the line it prints is marked and is not a bench value",
+    )
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
