@@ -105,6 +105,8 @@ SIGNATURES = {
     "dfb_int4_repack_k8": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_gemv_scratch_bytes": (c_sz, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "dfb_int4_gemv": (C.c_int, [C.POINTER(GemvDesc), c_vp]),
+    "dfb_int4_gemv_static_max_partials_bytes": (c_sz, []),
+    "dfb_int4_gemv_static": (C.c_int, [C.POINTER(GemvDesc), c_vp]),
     "dfb_rms_norm": (C.c_int, [c_vp, c_vp, c_f32, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_add_rms_norm": (C.c_int, [c_vp, c_vp, c_vp, c_f32, C.c_int, C.c_int, c_vp, c_vp, c_vp]),
     "dfb_silu_mul": (C.c_int, [c_vp, c_vp, c_i64, c_vp, c_vp]),

@@ -24,7 +24,9 @@
 // Bytes per launch (what the roofline is computed from): K*N/2 packed + K/group*N scale bytes
 // + rows*N*2 output; the activation vector is re-read from L2 by every CTA and is not counted.
 #include <algorithm>
+#include <mutex>
 
+#include "../../include/dfb200.h"
 #include "gemv_common.cuh"
 
 namespace dfb {
@@ -447,4 +449,125 @@ int launch_int4_dequant(const uint8_t* packed, const void* scale, int scale_bf16
   return check_launch("int4 dequant");
 }
 
+// ---- split-K GEMV on scratch the library owns (no allocation at call time) -----------------------
+//
+// The split-K kernel above, with its partial sums and arrival counters in a file-scope device array
+// instead of caller memory. The array's address is looked up once per device, on the first call with
+// that device current; later calls only clear the counters and launch.
+constexpr size_t STATIC_PARTIALS_BYTES = 2u << 20;  // 2 MiB of fp32 partial sums
+constexpr size_t STATIC_COUNTERS = 4096;            // arrival counters, one per (column tile, row block)
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_PARTIALS_BYTES + STATIC_COUNTERS * sizeof(unsigned);
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static void* g_static_ptr[STATIC_MAX_DEVICES];
+static std::mutex g_static_mutex;
+
+// Address of this device's copy of the array; looked up on first use (the current device's).
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_launch("static-scratch gemv: cudaGetDevice");
+  if (dev < 0 || dev >= STATIC_MAX_DEVICES) {
+    set_error("static-scratch gemv: device ordinal %d is beyond the %d this entry point tracks", dev, STATIC_MAX_DEVICES);
+    return 2;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("static-scratch gemv: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return 3;
+    }
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+
 }  // namespace dfb
+
+extern "C" size_t dfb_int4_gemv_static_max_partials_bytes(void) { return dfb::STATIC_PARTIALS_BYTES; }
+
+extern "C" int dfb_int4_gemv_static(const dfb_gemv_desc* d, void* stream) {
+  using namespace dfb;
+  if (!d) {
+    set_error("dfb_int4_gemv_static: null descriptor");
+    return 2;
+  }
+  if (d->rows < 0) {
+    set_error("dfb_int4_gemv_static: negative row count");
+    return 2;
+  }
+  if (d->rows == 0) return 0;
+  if (!d->x || !d->packed || !d->scale || !d->out) {
+    set_error("dfb_int4_gemv_static: null tensor pointer");
+    return 2;
+  }
+  if (int rc = check_int4_shape(d->K, d->N, d->group)) return rc;
+  if (d->group != 128 || d->K % 256 != 0 || d->N % 8 != 0 || ((uintptr_t)d->packed % 8) != 0) {
+    set_error("dfb_int4_gemv_static: serves the group-128 split-K kernel only (K %% 256 == 0, N %% 8 == 0, packed 8-byte "
+              "aligned); got K=%d N=%d group=%d", d->K, d->N, d->group);
+    return 2;
+  }
+  if (d->prologue < 0 || d->prologue > 2 || d->epilogue < 0 || d->epilogue > 2 || d->math < 0 || d->math > 2) {
+    set_error("dfb_int4_gemv_static: unknown prologue, epilogue or math mode (%d, %d, %d)", d->prologue, d->epilogue, d->math);
+    return 2;
+  }
+  if ((d->prologue == PRO_RMSNORM && !d->norm_w) || (d->prologue == PRO_SILU_MUL && !d->up) ||
+      (d->epilogue == EPI_RESIDUAL && !d->residual) ||
+      (d->epilogue == EPI_CONV && (!d->conv_state || !d->conv_w || d->conv_dim < 0 || d->conv_dim > d->N))) {
+    set_error("dfb_int4_gemv_static: the chosen prologue or epilogue lacks one of its tensors");
+    return 2;
+  }
+  const int rpc = rows_per_cta(d->rows);
+  const size_t partial_bytes = (size_t)d->rows * (d->K / 256) * d->N * sizeof(float);
+  const size_t counters = (size_t)((d->N + TN - 1) / TN) * ((d->rows + rpc - 1) / rpc);
+  if (partial_bytes > STATIC_PARTIALS_BYTES || counters > STATIC_COUNTERS) {
+    set_error("dfb_int4_gemv_static: rows=%d K=%d N=%d needs %zu bytes of partial sums and %zu counters; the built-in "
+              "scratch holds %zu bytes and %zu counters -- use dfb_int4_gemv with caller scratch for this size",
+              d->rows, d->K, d->N, partial_bytes, counters, (size_t)STATIC_PARTIALS_BYTES, (size_t)STATIC_COUNTERS);
+    return 2;
+  }
+  static const int configured = gemv_configure();
+  if (configured) return configured;
+  void* base = nullptr;
+  if (int rc = static_scratch_for_current_device(&base)) return rc;
+  GemvParams p = {};
+  p.x = (const bf16*)d->x;
+  p.x_stride = d->x_stride;
+  p.rows = d->rows;
+  p.packed = d->packed;
+  p.scale = d->scale;
+  p.scale_bf16 = d->scale_is_bf16;
+  p.K = d->K;
+  p.N = d->N;
+  p.group = d->group;
+  p.prologue = d->prologue;
+  p.norm_w = (const bf16*)d->norm_w;
+  p.eps = d->eps;
+  p.up = (const bf16*)d->up;
+  p.up_stride = d->up_stride;
+  p.epilogue = d->epilogue;
+  p.out = (bf16*)d->out;
+  p.out_stride = d->out_stride;
+  p.residual = (const bf16*)d->residual;
+  p.res_stride = d->residual_stride;
+  p.conv_state = (bf16*)d->conv_state;
+  p.conv_w = (const bf16*)d->conv_w;
+  p.conv_dim = d->conv_dim;
+  p.math = d->math;
+  p.partials = (float*)base;
+  p.counters = (unsigned*)((char*)base + STATIC_PARTIALS_BYTES);
+  p.force_tiled = 1;
+  // The last-arriver test counts from zero: clear this launch's counters in stream order. The partial
+  // sums need no clearing, every one that is read has been written by this launch.
+  if (cudaMemsetAsync(p.counters, 0, counters * sizeof(unsigned), (cudaStream_t)stream) != cudaSuccess)
+    return check_launch("dfb_int4_gemv_static: clearing the arrival counters");
+  switch (rpc) {
+    case 4: return launch_fast_math<4>(p, (cudaStream_t)stream);
+    case 2: return launch_fast_math<2>(p, (cudaStream_t)stream);
+    default: return launch_fast_math<1>(p, (cudaStream_t)stream);
+  }
+}

@@ -101,6 +101,23 @@ size_t dfb_int4_gemv_scratch_bytes(int rows, int K, int N, int group);
  * conv decode step (src/deltaforge/kernels/inline_causal_conv.py:98-129). */
 int dfb_int4_gemv(const dfb_gemv_desc* desc, void* stream);
 
+/* The same GEMV for callers that hold no device scratch: the split-K partial sums and arrival counters
+ * live in a device array that is part of the library image, so the call allocates nothing, on the host
+ * or the device. This entry point has no counterpart in the reference (its Triton GEMV takes its
+ * scratch from torch's allocator). It always runs the register-tiled split-K kernel, and serves only
+ * the group-128 layout (K % 256 == 0, N % 8 == 0); `scratch`, `scratch_bytes`, `force_tiled` and
+ * `packed_k8` of the descriptor are ignored. The built-in scratch holds
+ * dfb_int4_gemv_static_max_partials_bytes() (2 MiB) of partial sums, rows * (K/256) * N * 4 bytes per
+ * problem, and 4096 column-tile counters: every layer projection of the 4B decode step at one row
+ * fits, the LM head does not, and a problem beyond either limit is refused with DFB_ERR_ARG and a
+ * message that names both sizes. The first call on each device looks the array's address up (the
+ * device must be current); make that first call before any stream capture begins. Each call clears its
+ * counters in stream order before the launch. There is one array per device: two calls whose
+ * execution may overlap (different streams, or different host threads on different streams) race on
+ * it and give wrong sums, so callers serialise them on one stream. */
+size_t dfb_int4_gemv_static_max_partials_bytes(void);
+int dfb_int4_gemv_static(const dfb_gemv_desc* desc, void* stream);
+
 /* ---- elementwise ops with the reference's op contracts --------------------------------------- */
 
 /* deltaforge::rms_norm, src/deltaforge/kernels/fused_rmsnorm_residual.py:201-226. */
