@@ -169,8 +169,22 @@ def cpu_step_seconds(model, cache, head_fraction: int, repeats: int) -> list[flo
     return out
 
 
+def usable_host_cores() -> int:
+    """Cores this process may use: its affinity mask, capped by the cgroup CPU quota when there is one."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        quota, period = Path("/sys/fs/cgroup/cpu.max").read_text().split()[:2]
+        if quota != "max":
+            n = min(n, max(1, int(quota) // int(period)))
+    except (OSError, ValueError):
+        pass
+    return max(1, n)
+
+
 def run_cpu_port(steps: int, warmup: int, budget_s: float) -> dict:
     """Time the CPU port for ``steps`` steps after ``warmup``; the sample shrinks to fit ``budget_s``."""
+    # torchrun pins OMP_NUM_THREADS to 1; this arm runs on one rank alone and takes every host core
+    torch.set_num_threads(max(torch.get_num_threads(), usable_host_cores()))
     threads = torch.get_num_threads()
     head_fraction = 8
     model, cache, _ = cpu_sample_model(head_fraction)
@@ -211,6 +225,10 @@ def dist_setup(n_gpus: int):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch.distributed as dist
+
+        # NCCL prints its version banner on stdout at this level; stdout carries the one JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
 
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -433,6 +451,10 @@ def main() -> None:
         return
 
     line = run_ours(args)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
     if line is None:
         return
     if world == 1 and not args.no_cpu_baseline:
