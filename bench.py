@@ -289,7 +289,7 @@ def run_ours(args) -> dict | None:
     cache = E.DecodeCache(cfg, BATCH, CONTEXT + steps + warmup + 8, device=dev)
     synth.fill_cache(cache, CONTEXT, seed=77 + rank)
     snap = cache.snapshot()
-    eng = E.DecodeEngine(weights, cache)
+    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent")
     tok = torch.full((BATCH,), 1000 + rank, dtype=torch.int64, device=dev)
     eng.capture()
 
@@ -364,6 +364,7 @@ def run_ours(args) -> dict | None:
             "sequences": world * BATCH,
             "parallelism": f"independent sequences x{world}, no collectives",
             "l2": "each step streams 2.4 GB of weights, KV and state, 19x the 126 MB L2; no flush needed",
+            "engine": args.engine,
             "attn_splits": eng.attn_splits,
             "scale_dtype": "bf16",
         },
@@ -413,6 +414,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU port leg of the default run")
+    ap.add_argument("--engine", choices=("graph", "persistent"), default="graph",
+                    help="graph: one CUDA graph of kernels per token; persistent: one persistent kernel per token")
     ap.add_argument(
         "--layers",
         type=int,

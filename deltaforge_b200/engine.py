@@ -253,7 +253,17 @@ def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: i
 class DecodeEngine:
     """One model replica's decode step on one GPU, bound to one cache."""
 
-    def __init__(self, weights: ModelWeights, cache, *, attn_splits: int | None = None, math: int = MATH_FAST) -> None:
+    def __init__(
+        self,
+        weights: ModelWeights,
+        cache,
+        *,
+        attn_splits: int | None = None,
+        math: int = MATH_FAST,
+        persistent: bool = False,
+    ) -> None:
+        """``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
+        group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
         cfg = weights.config
         self.config, self.weights, self.cache = cfg, weights, cache
         self.batch, self.max_seq = cache.batch_size, cache.max_seq_len
@@ -275,7 +285,7 @@ class DecodeEngine:
             if not (qw.qweight.is_contiguous() and qw.scale.is_contiguous()):
                 raise ValueError("quantised weights must be contiguous")
             k, n = qw.in_features, qw.out_features
-            if qw.k8 is None and self.batch == 1 and qw.group_size == 128 and k % 256 == 0 and n % 4 == 0:
+            if qw.k8 is None and not persistent and self.batch == 1 and qw.group_size == 128 and k % 256 == 0 and n % 4 == 0:
                 from . import ops  # the re-packed copy the streaming GEMV reads; made once per weight
 
                 qw.k8 = ops.int4_repack_k8(qw.qweight)
@@ -317,6 +327,14 @@ class DecodeEngine:
         m.tokens, m.history, m.pos, m.logits = self.tokens.data_ptr(), self.history.data_ptr(), self.pos.data_ptr(), self.logits.data_ptr()
         m.attn_splits, m.math = self.attn_splits, math
         m.workspace, m.workspace_bytes = None, 0
+        m.persistent = int(persistent)
+        self.persistent = bool(persistent)
+        if persistent:
+            sbytes = self.lib.dfb_engine_weight_stream_bytes(C.byref(m))
+            if sbytes == 0:
+                raise ValueError("the persistent step supports batch 1 with group-128 int4 weights and 256-wide attention heads only")
+            self.weight_stream = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+            m.weight_stream, m.weight_stream_bytes = self.weight_stream.data_ptr(), sbytes
         nbytes = self.lib.dfb_engine_workspace_bytes(C.byref(m))
         self.workspace = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=dev)
         m.workspace, m.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()

@@ -127,10 +127,10 @@ def qwen_width_config(layers=4, vocab=4096) -> ModelConfig:
     )  # fmt: skip
 
 
-@pytest.mark.parametrize("math", [E.MATH_FAST, E.MATH_EXACT])
-def test_full_width_layers_match_oracle(math):
+@pytest.mark.parametrize("math,persistent", [(E.MATH_FAST, False), (E.MATH_EXACT, False), (E.MATH_FAST, True)])
+def test_full_width_layers_match_oracle(math, persistent):
     cfg = qwen_width_config()
-    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=4, max_seq=64, math=math)
+    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=4, max_seq=64, math=math, persistent=persistent)
     scale = ref.float().std().item()
     diff = (ref.float() - got.float()).abs()
     err = diff.max().item()
@@ -151,7 +151,9 @@ def test_full_width_layers_match_oracle(math):
     assert bool((ref.argmax(-1) == got.argmax(-1))[decisive].all())
     assert_caches_close(oc, cc, atol_state=2e-2 if math == E.MATH_EXACT else 2e-1)
     eng = cand.decode_engine(cc)
-    assert eng.launches_per_step == 1 + 4 * 5 + 3  # embed, 5 launches per layer of either kind, head + argmax + advance
+    eng.check_status()
+    # embed, 5 launches per layer of either kind, head + argmax + advance; or the one persistent kernel
+    assert eng.launches_per_step == (1 if persistent else 1 + 4 * 5 + 3)
 
 
 def test_graph_replay_equals_plain_launches_and_is_repeatable():
