@@ -142,7 +142,6 @@ struct PParams {
   u64 *H, *Pb, *O, *A, *SSQ, *AP, *ARG;
   unsigned* launch_counter;
   int* status;
-  int dbg;            // diagnostics: bit 0 skips the GEMV arithmetic (results are then meaningless)
   long long* trace;  // optional [P][32] device timestamps (ns) of the phases of layer trace_layer, or null
   int trace_layer;
 };
@@ -442,7 +441,7 @@ __device__ __forceinline__ void gemv_units(Ctx& cx, int G, int w, int gb, int ss
     const int ng = min(gpu, G - g0);
     const int s = cx.it % NSTAGE;
     const bool ok = ring_wait(cx, &cx.full[s], (cx.it / NSTAGE) & 1, 10);
-    if (ok && act && !(cx.p->dbg & 1)) {
+    if (ok && act) {
       const unsigned char* base = cx.ring + (size_t)s * STAGE;
 #pragma unroll 1
       for (int gl = glane; gl < ng; gl += GL) {
@@ -1098,7 +1097,6 @@ __global__ void __launch_bounds__(THREADS, 1) pstep_kernel(const __grid_constant
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
   Ctx cx;
-  cx.p = &p;
   cx.t = threadIdx.x;
   cx.warp = threadIdx.x >> 5;
   cx.lane = threadIdx.x & 31;
@@ -1129,6 +1127,13 @@ __global__ void __launch_bounds__(THREADS, 1) pstep_kernel(const __grid_constant
   q += 16;
   SliceGeo* geo_w = (SliceGeo*)q;
   cx.geo_s = geo_w;
+  q += NGEO * sizeof(SliceGeo);
+  // The parameters and the current layer's table entry are read through pointers by every phase: keep them
+  // in shared memory (a generic-address read of a kernel parameter or of the table costs a memory round trip).
+  PParams* sp = (PParams*)q;
+  q += (sizeof(PParams) + 15) & ~15;
+  PLayerDev* ls = (PLayerDev*)q;  // [2], the layer being computed and the next one
+  cx.p = sp;
   cx.it = 0;
   cx.w_ring = cx.w_ll = 0;
   cx.tslot = 0;
@@ -1141,6 +1146,9 @@ __global__ void __launch_bounds__(THREADS, 1) pstep_kernel(const __grid_constant
     *cx.failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (cx.t >= 32 && cx.t < 32 + (int)(sizeof(PParams) / 4)) ((uint32_t*)sp)[cx.t - 32] = ((const uint32_t*)&p)[cx.t - 32];
+  if (cx.t >= 128 && cx.t < 128 + (int)(sizeof(PLayerDev) / 4) && p.layers > 0)
+    ((uint32_t*)&ls[0])[cx.t - 128] = ((const uint32_t*)&p.L[0])[cx.t - 128];
   if (cx.t < NGEO) {
     // distinct projection shapes: the two kinds of input projection, hidden-wide outputs, gate|up, the head
     int items = 0, paired = 0;
@@ -1220,7 +1228,9 @@ __global__ void __launch_bounds__(THREADS, 1) pstep_kernel(const __grid_constant
   XSrc xs;
   mark(cx, 0);
   for (int li = 0; li < p.layers; ++li) {
-    const PLayerDev& L = p.L[li];
+    const PLayerDev& L = ls[li & 1];
+    if (li + 1 < p.layers && cx.t < (int)(sizeof(PLayerDev) / 4))  // visible long before the next layer starts
+      ((uint32_t*)&ls[(li + 1) & 1])[cx.t] = ((const uint32_t*)&p.L[li + 1])[cx.t];
     const bool attn = L.kind == DFB_LAYER_ATTENTION;
     const bool tr = li == p.trace_layer;
     if (tr) mark(cx, 1);
@@ -1404,7 +1414,8 @@ int sm_count_now() {
 }
 
 constexpr size_t SMEM_BYTES = (size_t)NSTAGE * STAGE + 33280 + MAX_HIDDEN * 4 + MAXGQ * HD * 4 + 2 * HD * 4 + 1024 * 4 + MAXW * 4 +
-                              16 * 4 + 2 * NSTAGE * 8 + 16 + NGEO * sizeof(SliceGeo) + 128;
+                              16 * 4 + 2 * NSTAGE * 8 + 16 + NGEO * sizeof(SliceGeo) + ((sizeof(PParams) + 15) & ~15) +
+                              2 * sizeof(PLayerDev) + 128;
 
 struct WsPlan {
   size_t H, Pb, O, A, SSQ, AP, ARG, counter, layers, bases, offsets, trace, total;
@@ -1550,7 +1561,6 @@ int pstep_create(const dfb_model_desc& m, void* ws, void* stream_mem, size_t str
   p.status = nullptr;  // set by the caller
   p.trace = nullptr;
   p.trace_layer = -1;
-  p.dbg = getenv("DFB_PSTEP_DBG") ? atoi(getenv("DFB_PSTEP_DBG")) : 0;
 
   // device tables
   std::vector<PLayerDev> layers(m.num_layers);

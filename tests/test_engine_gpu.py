@@ -191,6 +191,52 @@ def test_graph_replay_equals_plain_launches_and_is_repeatable():
     assert torch.equal(host.t().to(DEV), on_device)
 
 
+def test_persistent_engine_replays_and_matches_the_graph_engine():
+    """The one-kernel form of the step: graph replay == plain launches, greedy loop == stepping by hand, cache
+    restore between runs (the exchange buffers carry epochs, nothing needs clearing), and its logits within
+    bf16 noise of the multi-kernel engine's on the same weights and cache."""
+    cfg = qwen_width_config(layers=4, vocab=2048)
+    w = synth.random_model_weights(cfg, seed=3, device=DEV, scale_dtype=torch.bfloat16)
+    cache = E.DecodeCache(cfg, 1, 512, device=DEV)
+    synth.fill_cache(cache, 300, seed=5)
+    snap = cache.snapshot()
+    tok = torch.tensor([17], device=DEV)
+    ref_eng = E.DecodeEngine(w, cache)
+    want = [ref_eng.step(tok).clone()]
+    want.append(ref_eng.step(want[0].argmax(-1)).clone())
+    state_want = [t.clone() for t in cache.state_tensors()]
+    cache.restore(snap)
+    eng = E.DecodeEngine(w, cache, persistent=True)
+    assert eng.launches_per_step in (0, 1)
+    plain = [eng.step(tok, graph=False).clone()]
+    plain.append(eng.step(want[0].argmax(-1), graph=False).clone())
+    state_plain = [t.clone() for t in cache.state_tensors()]
+    eng.check_status()
+    cache.restore(snap)
+    graph = [eng.step(tok, graph=True).clone()]
+    graph.append(eng.step(want[0].argmax(-1), graph=True).clone())
+    for a, b in zip(plain, graph):
+        assert torch.equal(a, b)
+    for a, b in zip(state_plain, cache.state_tensors()):
+        assert torch.equal(a, b)
+    scale = want[0].float().std().item()
+    for a, b in zip(want, plain):
+        assert (a.float() - b.float()).abs().max().item() < 6e-2 * scale
+    for a, b in zip(state_want, state_plain):
+        assert (a.float() - b.float()).abs().max().item() <= 2e-2 + 2e-2 * a.float().abs().max().item()
+    cache.restore(snap)
+    by_hand, t = [], tok
+    for _ in range(5):
+        by_hand.append(eng.step(t).argmax(-1))
+        t = by_hand[-1]
+    cache.restore(snap)
+    on_device = eng.decode(tok, 5)
+    assert torch.equal(on_device, torch.stack(by_hand, dim=1))
+    assert cache.seq_len == 305
+    eng.check_status()
+    assert eng.launches_per_step == 1
+
+
 def test_capacity_is_checked_on_the_host():
     cfg = tiny_config()
     w = synth.random_model_weights(cfg, seed=1, device=DEV, scale_dtype=torch.float32)
