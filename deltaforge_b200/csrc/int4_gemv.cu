@@ -388,6 +388,7 @@ static int configure_rows() {
 int gemv_configure() {
   if (int rc = stream_configure()) return rc;
   if (int rc = cluster_configure()) return rc;
+  if (int rc = tc_configure()) return rc;
   if (int rc = configure_rows<1>()) return rc;
   if (int rc = configure_rows<2>()) return rc;
   return configure_rows<4>();
@@ -413,6 +414,8 @@ int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   if (p.rows <= 0 || p.N <= 0) return 0;
   static const int configured = gemv_configure();
   if (configured) return configured;
+  // eight rows and more: the weight tile is shared by enough rows for the tensor cores
+  if (!p.force_tiled && p.rows >= 8 && tc_path_ok(p)) return launch_gemm_tc(p, p.status, stream);
   if (!p.force_tiled && p.status) {
     // layer-sized matrices: one cluster per column tile; very wide ones (the LM head): persistent streaming
     if (p.N < 65536 && cluster_path_ok(p)) return launch_gemv_cluster(p, p.status, stream);

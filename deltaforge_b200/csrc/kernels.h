@@ -72,6 +72,10 @@ bool cluster_path_ok(const GemvParams& p);
 int cluster_configure();
 int launch_gemv_cluster(const GemvParams& p, int* status, cudaStream_t stream);
 int launch_gemv_stream(const GemvParams& p, int* status, cudaStream_t stream);
+// tensor-core (tcgen05) variant for 8..128 activation rows, on the re-packed weight
+bool tc_path_ok(const GemvParams& p);
+int tc_configure();
+int launch_gemm_tc(const GemvParams& p, int* status, cudaStream_t stream);
 // packed [K/2, N] bytes -> [K/8, N] words, word (kb, n) = the nibbles of column n, rows 8kb .. 8kb+7
 int launch_int4_repack_k8(const uint8_t* packed, int K, int N, uint32_t* out, cudaStream_t stream);
 
