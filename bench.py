@@ -423,7 +423,14 @@ def main() -> None:
         help="cut the model to this many layers (a multiple of 4) so that a profiler capture holds little device memory; "
         "the line it prints is marked and is not a bench value",
     )
+    ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 1: the metric's configuration)")
+    ap.add_argument("--context", type=int, default=None, help="tokens already in the cache (default 4096)")
     args = ap.parse_args()
+    global BATCH, CONTEXT, WORKLOAD
+    if args.batch is not None or args.context is not None:
+        BATCH = args.batch or BATCH
+        CONTEXT = args.context or CONTEXT
+        WORKLOAD = f"qwen3.5-4b int4 decode step, batch {BATCH}, ctx {CONTEXT} (not the metric's configuration)"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 

@@ -37,7 +37,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, pstep, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, pstep, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -80,6 +80,8 @@ Workspace plan(const dfb_model_desc& m) {
   w.am_ctr = take(B * 4);
   w.status = take(256);
   w.h_ss = take(256 * 4);
+  // batches of eight and more: the normalised / gated activation the tensor-core product reads
+  w.xn = take(m.batch >= 8 ? B * std::max(std::max((size_t)m.hidden, (size_t)m.intermediate), mixw) * 2 : 0);
   w.pstep = take(m.persistent ? pstep_workspace_bytes(m) : 0);
   w.total = off;
   return w;
@@ -99,6 +101,52 @@ struct Engine {
 
   int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
            long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
+    if (m.batch >= 8 && l.packed_k8 && m.math != MATH_FAST_HALF2) {
+      // Tensor-core path: prologue and the conv epilogue run as their own small kernels around the product.
+      GemvParams q = {};
+      q.x = x;
+      q.x_stride = x_stride;
+      if (prologue == PRO_RMSNORM) {
+        if (x_stride != l.K) {
+          set_error("engine: RMSNorm prologue expects contiguous rows");
+          return DFB_ERR_ARG;
+        }
+        if (int rc = launch_rms_norm(x, (const bf16*)norm_w, m.eps, m.batch, l.K, (bf16*)at(ws.xn), s)) return rc;
+        ++launches;
+        q.x = (const bf16*)at(ws.xn);
+        q.x_stride = l.K;
+      } else if (prologue == PRO_SILU_MUL) {
+        if (int rc = launch_silu_mul_rows(x, up, x_stride, m.batch, l.K, (bf16*)at(ws.xn), s)) return rc;
+        ++launches;
+        q.x = (const bf16*)at(ws.xn);
+        q.x_stride = l.K;
+      }
+      q.rows = m.batch;
+      q.packed = l.packed;
+      q.packed_k8 = (const uint32_t*)l.packed_k8;
+      q.scale = l.scale;
+      q.scale_bf16 = l.scale_is_bf16;
+      q.K = l.K, q.N = l.N, q.group = l.group;
+      q.prologue = PRO_NONE;
+      q.epilogue = epilogue == EPI_RESIDUAL ? EPI_RESIDUAL : EPI_STORE;
+      q.out = out, q.out_stride = out_stride;
+      q.residual = out, q.res_stride = out_stride;
+      q.partials = (float*)at(ws.partials);
+      q.counters = (unsigned*)at(ws.counters);
+      q.math = m.math;
+      q.status = (int*)at(ws.status);
+      if (tc_path_ok(q)) {
+        ss_valid = false;
+        ++launches;
+        if (int rc = launch_gemv(q, s)) return rc;
+        if (conv_layer) {
+          ++launches;
+          return launch_causal_conv_rows(out, out_stride, (bf16*)conv_layer->conv_state, (const bf16*)conv_layer->conv_w, m.batch,
+                                         2 * m.lin_k_heads * m.lin_dk + m.lin_v_heads * m.lin_dv, s);
+        }
+        return 0;
+      }
+    }
     const bool x_is_h = (const void*)x == (const void*)at(ws.h);
     GemvParams p = {};
     p.x = x;

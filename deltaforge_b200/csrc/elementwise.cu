@@ -84,6 +84,35 @@ __global__ void causal_conv_step_kernel(const bf16* x, bf16* cache, const bf16* 
   st[2] = xv;
 }
 
+// Row-strided forms for the batched decode step: gate | up live side by side in one projection row, and
+// the conv runs in place on the leading channels of the input-projection row.
+__global__ void silu_mul_rows_kernel(const bf16* gate, const bf16* up, long in_stride, int n, long total, bf16* out) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long r = i / n, c = i % n;
+  const float s = round_bf16(silu_f(bf2f(gate[r * in_stride + c])));
+  out[i] = f2bf(__fmul_rn(s, bf2f(up[r * in_stride + c])));
+}
+
+__global__ void causal_conv_rows_kernel(bf16* x, long x_stride, bf16* cache, const bf16* w, int channels, long total) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long r = i / channels;
+  const int c = (int)(i % channels);
+  bf16* st = cache + i * 3;
+  const bf16* wc = w + (long)c * 4;
+  bf16* xp = x + r * x_stride + c;
+  const bf16 xv = *xp;
+  float acc = __fmul_rn(bf2f(st[0]), bf2f(wc[0]));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(st[1]), bf2f(wc[1])));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(st[2]), bf2f(wc[2])));
+  acc = __fadd_rn(acc, __fmul_rn(bf2f(xv), bf2f(wc[3])));
+  *xp = f2bf(silu_f(round_bf16(acc)));
+  st[0] = st[1];
+  st[1] = st[2];
+  st[2] = xv;
+}
+
 // Row gather of the embedding table (src/deltaforge/reference.py:804).
 __global__ void __launch_bounds__(128) embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out, float* ss_out,
                                                     int ss_count) {
@@ -210,6 +239,20 @@ int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch
   if (total <= 0) return 0;
   causal_conv_step_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, cache, w, channels, total, out);
   return check_launch("causal_conv_step");
+}
+
+int launch_silu_mul_rows(const bf16* gate, const bf16* up, long in_stride, int rows, int n, bf16* out, cudaStream_t s) {
+  const long total = (long)rows * n;
+  if (total <= 0) return 0;
+  silu_mul_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(gate, up, in_stride, n, total, out);
+  return check_launch("silu_mul (rows)");
+}
+
+int launch_causal_conv_rows(bf16* x, long x_stride, bf16* cache, const bf16* w, int rows, int channels, cudaStream_t s) {
+  const long total = (long)rows * channels;
+  if (total <= 0) return 0;
+  causal_conv_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, x_stride, cache, w, channels, total);
+  return check_launch("causal_conv_step (rows)");
 }
 
 int elementwise_configure() {

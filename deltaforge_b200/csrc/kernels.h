@@ -194,6 +194,10 @@ int launch_partial_rope(const bf16* x, const bf16* cos, const bf16* sin, int bat
                         bf16* out, cudaStream_t s);
 int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch, int channels, bf16* out,
                             cudaStream_t s);
+// gate and up are rows of one buffer (in_stride apart), out is [rows, n] contiguous
+int launch_silu_mul_rows(const bf16* gate, const bf16* up, long in_stride, int rows, int n, bf16* out, cudaStream_t s);
+// conv + SiLU in place on the first `channels` entries of every row of x; cache [rows, channels, 3]
+int launch_causal_conv_rows(bf16* x, long x_stride, bf16* cache, const bf16* w, int rows, int channels, cudaStream_t s);
 // Row gather; when ss_out is given (batch 1) also stores the row's sum of squares in ss_out[0] and zeros ss_out[1..ss_count).
 int launch_embed(const bf16* table, const int64_t* tokens, int batch, int hidden, bf16* out, float* ss_out, int ss_count,
                  cudaStream_t s);

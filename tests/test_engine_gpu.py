@@ -156,6 +156,24 @@ def test_full_width_layers_match_oracle(math, persistent):
     assert eng.launches_per_step == (1 if persistent else 1 + 4 * 5 + 3)
 
 
+def test_batch_of_eight_runs_the_tensor_core_projections_and_matches_oracle():
+    """Eight sequences: every projection goes through the tcgen05 product (weights dequantised to exactly the
+    reference's bf16 values), with the norm / SwiGLU / conv steps as separate kernels around it."""
+    cfg = qwen_width_config(layers=4, vocab=2048)
+    ref, got, oc, cc, cand = run_pair(cfg, batch=8, prompt_len=3, steps=3, max_seq=64)
+    scale = ref.float().std().item()
+    diff = (ref.float() - got.float()).abs()
+    assert diff.max().item() < 8e-2 * scale
+    assert diff.pow(2).mean().sqrt().item() < 1.5e-2 * scale
+    kl, agree = kl_and_agreement(ref, got)
+    assert kl < 2e-4, kl
+    assert_caches_close(oc, cc, atol_state=2e-2)
+    eng = cand.decode_engine(cc)
+    eng.check_status()
+    # embed; per layer 4 products + 2 norms + silu-mul + mixer (+ conv on DeltaNet layers); final norm, head, argmax, advance
+    assert eng.launches_per_step == 1 + 3 * 9 + 8 + 4
+
+
 def test_graph_replay_equals_plain_launches_and_is_repeatable():
     cfg = qwen_width_config(layers=4, vocab=2048)
     w = synth.random_model_weights(cfg, seed=3, device=DEV, scale_dtype=torch.float32)
