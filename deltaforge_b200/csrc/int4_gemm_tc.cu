@@ -201,12 +201,19 @@ __global__ void __launch_bounds__(TC_THREADS, 2) int4_gemm_tc_kernel(const __gri
     // ---------------- dequant warps: packed words -> the bf16 A tile the reference would hold ----------------
     const int n = t & (TM - 1), half = t >> 7;  // column of the slab; word rows half*4 .. half*4+3 of the block
     const bool col_ok = n0 + n < p.N;
-    float sc = 0.f;
+    // a scale group is two k blocks; the next group's scale is requested a group ahead of its use
+    const int last_group = (kb1 - 1) >> 1;
+    float sc = col_ok && nblocks > 0 ? load_scale(p, (long)(kb0 >> 1) * p.N + n0 + n) : 0.f;
+    float sc_next = sc;
     bool ok = true;
     for (int i = 0; i < nblocks; ++i) {
       const int s = i % a.stages;
       const int kb = kb0 + i;
-      if (i == 0 || (kb & 1) == 0) sc = col_ok ? load_scale(p, (long)(kb >> 1) * p.N + n0 + n) : 0.f;  // group = 2 blocks
+      if (i > 0 && (kb & 1) == 0) sc = sc_next;
+      if (i == 0 || (kb & 1) == 0) {
+        const int g_next = (kb >> 1) + 1;
+        if (col_ok && g_next <= last_group) sc_next = load_scale(p, (long)g_next * p.N + n0 + n);
+      }
       ok = tc_wait(&full[s], (i / a.stages) & 1, failed, a.status, 34);
       if (!ok) break;
       unsigned char* st = sm + (size_t)s * stage_bytes;

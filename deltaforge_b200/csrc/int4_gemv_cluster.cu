@@ -300,8 +300,6 @@ EncodeTiledFn encode_fn() {
 
 int pick_cs(int K) {
   const int G = K / 128;
-  static const int env_cs = getenv("DFB_CLUSTER_CS") ? atoi(getenv("DFB_CLUSTER_CS")) : 0;
-  if (env_cs > 0) return std::max(1, std::min(std::min(MAX_CS, env_cs), G));
   // Measured on B200: with K = 2560 (20 groups) clusters of 4 with 5 groups per CTA beat clusters of 8
   // (fewer CTAs repeat the prologue, smaller clusters are scheduled sooner); the deeper matrices
   // (K = 4096, 9216) need 8 CTAs per tile to keep a CTA's units within shared memory and the SMs busy.

@@ -417,13 +417,11 @@ int launch_stream_rbk(const GemvParams& p, int* status, cudaStream_t stream) {
   a.rbc = (p.K / 8) / RBK;
   a.units = a.tiles * a.rbc;
   a.stages = pick_stages(p.K, RBK);
-  static const int env_stages = getenv("DFB_STREAM_STAGES") ? atoi(getenv("DFB_STREAM_STAGES")) : 0;
   // three CTAs per SM: 24 consumer warps hide the shared-memory and dp4a latencies one CTA cannot
-  static const int env_mult = getenv("DFB_STREAM_CTAS_PER_SM") ? atoi(getenv("DFB_STREAM_CTAS_PER_SM")) : 3;
-  if (env_stages > 0) a.stages = env_stages;
+  constexpr int CTAS_PER_SM = 3;
   a.status = status;
   a.max_slots = stream_max_slots(p.K, p.N);
-  const int P = std::min(sm_count() * env_mult, a.units);
+  const int P = std::min(sm_count() * CTAS_PER_SM, a.units);
   const size_t smem = smem_needed(p.K, RBK, a.stages);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(P, 1, 1);
