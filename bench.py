@@ -407,6 +407,70 @@ def run_ours(args) -> dict | None:
     return line
 
 
+def run_tp(args) -> dict | None:
+    """All ranks of the job form ONE tensor-parallel replica decoding one batch (BASELINE configs[4])."""
+    from deltaforge_b200 import engine as E
+    from deltaforge_b200 import qwen3_5_4b_config, synth
+    from deltaforge_b200 import tp as TP
+    from deltaforge_b200.bytes_model import decode_bytes_per_step
+
+    dist, rank, world, local = dist_setup(args.gpus)
+    if dist is None:
+        raise RuntimeError("--tp needs a multi-rank launch (torchrun)")
+    dev = torch.device("cuda", local)
+    cfg = qwen3_5_4b_config() if args.layers is None else qwen3_5_4b_config(num_hidden_layers=args.layers)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    full = synth.random_model_weights(cfg, seed=1234, device=dev, scale_dtype=torch.bfloat16)  # same seed on every rank
+    shard = TP.shard_weights(full, rank, world)
+    del full
+    torch.cuda.empty_cache()
+    cache = E.DecodeCache(TP.shard_config(cfg, world), BATCH, CONTEXT + steps + warmup + 8, device=dev)
+    synth.fill_cache(cache, CONTEXT, seed=77)
+    eng = TP.TensorParallelEngine(shard, cache, rank=rank, tp=world)
+    tok = torch.full((BATCH,), 1000, dtype=torch.int64, device=dev)
+    eng.decode(tok, warmup)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        e0.record()
+        eng.decode(tok, steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    dist.barrier()
+    times = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    eng.engine.check_status()
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peaks()
+    ms_max = times.item()
+    bytes_step = decode_bytes_per_step(cfg, batch=BATCH, context=CONTEXT, scale_bytes=2)
+    return {
+        "metric": METRIC,
+        "value": BATCH * steps / (ms_max / 1e3),
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": ms_max / steps,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "int4 weights, bf16 activations, fp32 accumulate and recurrent state",
+        "data": "synthetic",
+        "config": {
+            "workload": f"qwen3.5-4b int4 decode step, batch {BATCH}, ctx {CONTEXT}, ONE replica tensor-parallel over {world} GPUs",
+            "parallelism": f"tp{world}: heads, MLP channels and vocabulary sharded; two fp32 all-reduces (NCCL) per layer",
+            "all_reduces_per_token": 2 * cfg.num_hidden_layers,
+        },
+        "clocks": clocks.summary(),
+        "roofline_step": {"bytes_per_token": bytes_step["total"], "achieved": bytes_step["total"] / (ms_max / steps * 1e-3) / 1e9,
+                          "peak": peak * world, "unit": "GB/s", "peak_kind": f"of {peak_kind}, x{world} GPUs"},
+    }
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -423,6 +487,7 @@ def main() -> None:
         help="cut the model to this many layers (a multiple of 4) so that a profiler capture holds little device memory; "
         "the line it prints is marked and is not a bench value",
     )
+    ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 1: the metric's configuration)")
     ap.add_argument("--context", type=int, default=None, help="tokens already in the cache (default 4096)")
     args = ap.parse_args()
@@ -460,7 +525,7 @@ def main() -> None:
         print(json.dumps(line), flush=True)
         return
 
-    line = run_ours(args)
+    line = run_tp(args) if args.tp else run_ours(args)
     if world > 1:
         import torch.distributed as dist
 

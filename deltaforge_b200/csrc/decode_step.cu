@@ -37,7 +37,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, pstep, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, ar, pstep, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -82,6 +82,7 @@ Workspace plan(const dfb_model_desc& m) {
   w.h_ss = take(256 * 4);
   // batches of eight and more: the normalised / gated activation the tensor-core product reads
   w.xn = take(m.batch >= 8 ? B * std::max(std::max((size_t)m.hidden, (size_t)m.intermediate), mixw) * 2 : 0);
+  w.ar = take(m.tp_size > 1 ? B * m.hidden * 4 : 0);
   w.pstep = take(m.persistent ? pstep_workspace_bytes(m) : 0);
   w.total = off;
   return w;
@@ -101,7 +102,7 @@ struct Engine {
 
   int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
            long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
-    if (m.batch >= 8 && l.packed_k8 && m.math != MATH_FAST_HALF2) {
+    if (m.batch >= 8 && l.packed_k8 && m.math != MATH_FAST_HALF2 && epilogue != EPI_PARTIAL_F32) {
       // Tensor-core path: prologue and the conv epilogue run as their own small kernels around the product.
       GemvParams q = {};
       q.x = x;
@@ -192,183 +193,233 @@ struct Engine {
     return launch_gemv(p, s);
   }
 
+  // ---- the token mixers ------------------------------------------------------------------------------------
+  int mixer_deltanet(const dfb_layer_desc& L, bf16* proj, long pstride, bf16* mix, cudaStream_t s) {
+    const int kd = m.lin_k_heads * m.lin_dk, vd = m.lin_v_heads * m.lin_dv;
+    DeltaNetParams d = {};
+    d.batch = m.batch;
+    d.num_k_heads = m.lin_k_heads;
+    d.num_v_heads = m.lin_v_heads;
+    d.dk = m.lin_dk;
+    d.dv = m.lin_dv;
+    d.q = proj;
+    d.k = proj + kd;
+    d.v = proj + 2 * kd;
+    d.z = proj + 2 * kd + vd;
+    d.b = proj + 2 * kd + 2 * vd;
+    d.a = proj + 2 * kd + 2 * vd + m.lin_v_heads;
+    d.row_stride = pstride;
+    d.a_log = L.a_log;
+    d.dt_bias = L.dt_bias;
+    d.norm_w = L.gnorm_w;
+    d.norm_w_bf16 = L.gnorm_w_is_bf16;
+    d.eps = m.eps;
+    d.state = L.recurrent;
+    d.out = mix;
+    d.out_stride = vd;
+    ++launches;
+    return launch_deltanet_step(d, s);
+  }
+
+  int mixer_attention(const dfb_layer_desc& L, bf16* proj, long pstride, bf16* mix, bf16* qout, cudaStream_t s) {
+    const int d_ = m.head_dim;
+    const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
+    if (attn_step_ok(d_, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) {
+      // norms, RoPE, KV write, split-KV decode, merge and gate in one launch
+      AttnStepParams q = {};
+      q.batch = m.batch;
+      q.hq = m.hq;
+      q.hkv = m.hkv;
+      q.d = d_;
+      q.rotary_dim = m.rotary_dim;
+      q.proj = proj;
+      q.proj_stride = pstride;
+      q.q_norm_w = (const bf16*)L.q_norm_w;
+      q.k_norm_w = (const bf16*)L.k_norm_w;
+      q.eps = m.eps;
+      q.inv_freq = m.inv_freq;
+      q.pos = m.pos;
+      q.kcache = (bf16*)L.kcache;
+      q.vcache = (bf16*)L.vcache;
+      q.kv_batch_stride = kvb;
+      q.kv_head_stride = kvh;
+      q.max_seq = m.max_seq;
+      q.attn_output_gate = m.attn_output_gate;
+      q.gate_swish = m.gate_is_swish;
+      q.scale = 1.0f / sqrtf((float)d_);
+      q.splits = m.attn_splits;
+      q.cluster_size = std::min(m.attn_splits, 4);  // these CTAs fill an SM each: small clusters schedule sooner
+      if (m.attn_splits > 1) {
+        char* sc = at(ws.attn);
+        q.part_acc = (float*)sc;
+        sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
+        q.part_ml = (float*)sc;
+        sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
+        q.counters = (unsigned*)sc;
+      }
+      q.out = mix;
+      q.out_stride = (long)m.hq * d_;
+      q.status = (int*)at(ws.status);
+      ++launches;
+      return launch_attn_step(q, s);
+    }
+    AttnPrepParams pp = {};
+    pp.batch = m.batch;
+    pp.hq = m.hq;
+    pp.hkv = m.hkv;
+    pp.d = d_;
+    pp.rotary_dim = m.rotary_dim;
+    pp.proj = proj;
+    pp.proj_stride = pstride;
+    pp.q_norm_w = (const bf16*)L.q_norm_w;
+    pp.k_norm_w = (const bf16*)L.k_norm_w;
+    pp.eps = m.eps;
+    pp.inv_freq = m.inv_freq;
+    pp.pos = m.pos;
+    pp.q_out = qout;
+    pp.kcache = (bf16*)L.kcache;
+    pp.vcache = (bf16*)L.vcache;
+    pp.kv_batch_stride = kvb;
+    pp.kv_head_stride = kvh;
+    pp.attn_output_gate = m.attn_output_gate;
+    pp.max_seq = m.max_seq;
+    ++launches;
+    if (int rc = launch_attn_prep(pp, s)) return rc;
+    AttnParams a = {};
+    a.batch = m.batch;
+    a.hq = m.hq;
+    a.hkv = m.hkv;
+    a.d = d_;
+    a.q = qout;
+    a.q_stride = (long)m.hq * d_;
+    a.qh_stride = d_;
+    a.kcache = (const bf16*)L.kcache;
+    a.vcache = (const bf16*)L.vcache;
+    a.kv_batch_stride = kvb;
+    a.kv_head_stride = kvh;
+    a.pos = m.pos;
+    a.key_len = m.max_seq;  // capacity; the live length is *pos + 1
+    a.scale = 1.0f / sqrtf((float)d_);
+    a.splits = m.attn_splits;
+    if (m.attn_splits > 1) {
+      char* sc = at(ws.attn);
+      a.part_acc = (float*)sc;
+      sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
+      a.part_ml = (float*)sc;
+      sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
+      a.counters = (unsigned*)sc;
+    }
+    if (m.attn_output_gate) {
+      a.gate = proj + d_;
+      a.gate_stride = pstride;
+      a.gateh_stride = 2 * d_;
+      a.gate_swish = m.gate_is_swish;
+    }
+    a.out = mix;
+    a.out_stride = (long)m.hq * d_;
+    ++launches;
+    return launch_attn_decode(a, s);
+  }
+
+  // ---- the step, in halves of a layer ----------------------------------------------------------------------
+  // With tensor parallelism (tp_size > 1) the K-sharded projections at the end of each half leave fp32 partial
+  // sums in the `ar` buffer instead of adding into the residual stream; the caller all-reduces that buffer
+  // between segments and the next segment starts with the residual add.
+  bool tp() const { return m.tp_size > 1; }
+  int num_segments() const { return tp() ? 2 * m.num_layers + 1 : 1; }
+
+  int first_half(int i, cudaStream_t s) {  // input projections, token mixer, output projection
+    const dfb_layer_desc& L = layers[i];
+    bf16* h = (bf16*)at(ws.h);
+    bf16* proj = (bf16*)at(ws.proj);
+    bf16* mix = (bf16*)at(ws.mix);
+    const int H = m.hidden;
+    const long pstride = L.in_proj.N;
+    const bool dn = L.kind == DFB_LAYER_DELTANET;
+    int rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, dn ? EPI_CONV : EPI_STORE, proj, pstride, dn ? &L : nullptr, s);
+    if (rc) return rc;
+    rc = dn ? mixer_deltanet(L, proj, pstride, mix, s) : mixer_attention(L, proj, pstride, mix, (bf16*)at(ws.qout), s);
+    if (rc) return rc;
+    const long mixw = dn ? (long)m.lin_v_heads * m.lin_dv : (long)m.hq * m.head_dim;
+    if (tp()) return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
+    return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+  }
+
+  int second_half(int i, cudaStream_t s) {  // SwiGLU MLP
+    const dfb_layer_desc& L = layers[i];
+    bf16* h = (bf16*)at(ws.h);
+    bf16* gu = (bf16*)at(ws.gu);
+    const int H = m.hidden, I = m.intermediate;
+    int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
+    if (rc) return rc;
+    if (tp()) return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
+    return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
+  }
+
+  int head_and_pick(cudaStream_t s) {
+    bf16* h = (bf16*)at(ws.h);
+    int rc = gemv(m.head, h, m.hidden, PRO_RMSNORM, m.final_norm_w, nullptr, 0, EPI_STORE, (bf16*)m.logits, m.vocab, nullptr, s);
+    if (rc) return rc;
+    if (!tp()) {  // with a sharded vocabulary the caller picks the token across ranks
+      rc = launch_argmax((const bf16*)m.logits, m.batch, m.vocab, m.vocab, m.tokens, m.history, m.pos, (float*)at(ws.am_val),
+                         (int*)at(ws.am_idx), (unsigned*)at(ws.am_ctr), s);
+      ++launches;
+      if (rc) return rc;
+    }
+    rc = launch_advance(m.pos, 1, s);
+    ++launches;
+    return rc;
+  }
+
+  int embed(cudaStream_t s) {
+    const int H = m.hidden;
+    const int h_tiles = (H + cluster_tile_width(H) - 1) / cluster_tile_width(H);
+    ss_valid = m.batch == 1 && h_tiles <= 256 && !tp();
+    ++launches;
+    return launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, (bf16*)at(ws.h), ss_valid ? (float*)at(ws.h_ss) : nullptr, h_tiles, s);
+  }
+
+  int add_partial(cudaStream_t s) {
+    ss_valid = false;
+    ++launches;
+    return launch_add_partial((bf16*)at(ws.h), (const float*)at(ws.ar), (long)m.batch * m.hidden, s);
+  }
+
+  // Segment `seg` of a tensor-parallel step: 0 = embedding + first half of layer 0; 2l+1 = second half of
+  // layer l; 2l+2 = first half of layer l+1; the last = head. Every segment but the first begins with the
+  // residual add of the all-reduced buffer.
+  int step_segment(int seg, cudaStream_t s) {
+    if (!tp() || seg < 0 || seg >= num_segments()) {
+      set_error("engine: segment %d of %d (tensor-parallel engines only)", seg, num_segments());
+      return DFB_ERR_ARG;
+    }
+    if (seg == 0) launches = 0;
+    if (seg == 0) {
+      if (int rc = embed(s)) return rc;
+    } else {
+      if (int rc = add_partial(s)) return rc;
+    }
+    if (seg == 2 * m.num_layers) return head_and_pick(s);
+    if (seg & 1) return second_half(seg / 2, s);
+    return first_half(seg / 2, s);
+  }
+
   int step(cudaStream_t s) {
     if (ps) {
       launches = 1;
       return pstep_launch(ps, s);
     }
-    launches = 0;
-    bf16* h = (bf16*)at(ws.h);
-    bf16* proj = (bf16*)at(ws.proj);
-    bf16* mix = (bf16*)at(ws.mix);
-    bf16* qout = (bf16*)at(ws.qout);
-    bf16* gu = (bf16*)at(ws.gu);
-    const int H = m.hidden, I = m.intermediate;
-    const int h_tiles = (H + cluster_tile_width(H) - 1) / cluster_tile_width(H);
-    ss_valid = m.batch == 1 && h_tiles <= 256;
-    int rc = launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, h, ss_valid ? (float*)at(ws.h_ss) : nullptr, h_tiles, s);
-    ++launches;
-    if (rc) return rc;
-    for (int i = 0; i < m.num_layers; ++i) {
-      const dfb_layer_desc& L = layers[i];
-      const long pstride = L.in_proj.N;
-      if (L.kind == DFB_LAYER_DELTANET) {
-        rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, EPI_CONV, proj, pstride, &L, s);
-        if (rc) return rc;
-        const int kd = m.lin_k_heads * m.lin_dk, vd = m.lin_v_heads * m.lin_dv;
-        DeltaNetParams d = {};
-        d.batch = m.batch;
-        d.num_k_heads = m.lin_k_heads;
-        d.num_v_heads = m.lin_v_heads;
-        d.dk = m.lin_dk;
-        d.dv = m.lin_dv;
-        d.q = proj;
-        d.k = proj + kd;
-        d.v = proj + 2 * kd;
-        d.z = proj + 2 * kd + vd;
-        d.b = proj + 2 * kd + 2 * vd;
-        d.a = proj + 2 * kd + 2 * vd + m.lin_v_heads;
-        d.row_stride = pstride;
-        d.a_log = L.a_log;
-        d.dt_bias = L.dt_bias;
-        d.norm_w = L.gnorm_w;
-        d.norm_w_bf16 = L.gnorm_w_is_bf16;
-        d.eps = m.eps;
-        d.state = L.recurrent;
-        d.out = mix;
-        d.out_stride = vd;
-        rc = launch_deltanet_step(d, s);
-        ++launches;
-        if (rc) return rc;
-        rc = gemv(L.out_proj, mix, vd, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
-        if (rc) return rc;
-      } else {
-        rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, EPI_STORE, proj, pstride, nullptr, s);
-        if (rc) return rc;
-        const int d_ = m.head_dim;
-        const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
-        if (attn_step_ok(d_, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) {
-          // norms, RoPE, KV write, split-KV decode, merge and gate in one launch
-          AttnStepParams q = {};
-          q.batch = m.batch;
-          q.hq = m.hq;
-          q.hkv = m.hkv;
-          q.d = d_;
-          q.rotary_dim = m.rotary_dim;
-          q.proj = proj;
-          q.proj_stride = pstride;
-          q.q_norm_w = (const bf16*)L.q_norm_w;
-          q.k_norm_w = (const bf16*)L.k_norm_w;
-          q.eps = m.eps;
-          q.inv_freq = m.inv_freq;
-          q.pos = m.pos;
-          q.kcache = (bf16*)L.kcache;
-          q.vcache = (bf16*)L.vcache;
-          q.kv_batch_stride = kvb;
-          q.kv_head_stride = kvh;
-          q.max_seq = m.max_seq;
-          q.attn_output_gate = m.attn_output_gate;
-          q.gate_swish = m.gate_is_swish;
-          q.scale = 1.0f / sqrtf((float)d_);
-          q.splits = m.attn_splits;
-          q.cluster_size = std::min(m.attn_splits, 4);  // these CTAs fill an SM each: small clusters schedule sooner
-          if (m.attn_splits > 1) {
-            char* sc = at(ws.attn);
-            q.part_acc = (float*)sc;
-            sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
-            q.part_ml = (float*)sc;
-            sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
-            q.counters = (unsigned*)sc;
-          }
-          q.out = mix;
-          q.out_stride = (long)m.hq * d_;
-          q.status = (int*)at(ws.status);
-          rc = launch_attn_step(q, s);
-          ++launches;
-          if (rc) return rc;
-          rc = gemv(L.out_proj, mix, (long)m.hq * d_, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
-          if (rc) return rc;
-          rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
-          if (rc) return rc;
-          rc = gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
-          if (rc) return rc;
-          continue;
-        }
-        AttnPrepParams pp = {};
-        pp.batch = m.batch;
-        pp.hq = m.hq;
-        pp.hkv = m.hkv;
-        pp.d = d_;
-        pp.rotary_dim = m.rotary_dim;
-        pp.proj = proj;
-        pp.proj_stride = pstride;
-        pp.q_norm_w = (const bf16*)L.q_norm_w;
-        pp.k_norm_w = (const bf16*)L.k_norm_w;
-        pp.eps = m.eps;
-        pp.inv_freq = m.inv_freq;
-        pp.pos = m.pos;
-        pp.q_out = qout;
-        pp.kcache = (bf16*)L.kcache;
-        pp.vcache = (bf16*)L.vcache;
-        pp.kv_batch_stride = kvb;
-        pp.kv_head_stride = kvh;
-        pp.attn_output_gate = m.attn_output_gate;
-        pp.max_seq = m.max_seq;
-        rc = launch_attn_prep(pp, s);
-        ++launches;
-        if (rc) return rc;
-        AttnParams a = {};
-        a.batch = m.batch;
-        a.hq = m.hq;
-        a.hkv = m.hkv;
-        a.d = d_;
-        a.q = qout;
-        a.q_stride = (long)m.hq * d_;
-        a.qh_stride = d_;
-        a.kcache = (const bf16*)L.kcache;
-        a.vcache = (const bf16*)L.vcache;
-        a.kv_batch_stride = kvb;
-        a.kv_head_stride = kvh;
-        a.pos = m.pos;
-        a.key_len = m.max_seq;  // capacity; the live length is *pos + 1
-        a.scale = 1.0f / sqrtf((float)d_);
-        a.splits = m.attn_splits;
-        if (m.attn_splits > 1) {
-          char* sc = at(ws.attn);
-          a.part_acc = (float*)sc;
-          sc += align_up((size_t)m.batch * m.hq * m.attn_splits * d_ * 4, 256);
-          a.part_ml = (float*)sc;
-          sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
-          a.counters = (unsigned*)sc;
-        }
-        if (m.attn_output_gate) {
-          a.gate = proj + d_;
-          a.gate_stride = pstride;
-          a.gateh_stride = 2 * d_;
-          a.gate_swish = m.gate_is_swish;
-        }
-        a.out = mix;
-        a.out_stride = (long)m.hq * d_;
-        rc = launch_attn_decode(a, s);
-        ++launches;
-        if (rc) return rc;
-        rc = gemv(L.out_proj, mix, (long)m.hq * d_, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
-        if (rc) return rc;
-      }
-      rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
-      if (rc) return rc;
-      rc = gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
-      if (rc) return rc;
+    if (tp()) {
+      set_error("engine: a tensor-parallel step is run segment by segment, with an all-reduce of the partial buffer in between");
+      return DFB_ERR_ARG;
     }
-    rc = gemv(m.head, h, H, PRO_RMSNORM, m.final_norm_w, nullptr, 0, EPI_STORE, (bf16*)m.logits, m.vocab, nullptr, s);
-    if (rc) return rc;
-    rc = launch_argmax((const bf16*)m.logits, m.batch, m.vocab, m.vocab, m.tokens, m.history, m.pos, (float*)at(ws.am_val),
-                       (int*)at(ws.am_idx), (unsigned*)at(ws.am_ctr), s);
-    ++launches;
-    if (rc) return rc;
-    rc = launch_advance(m.pos, 1, s);
-    ++launches;
-    return rc;
+    launches = 0;
+    if (int rc = embed(s)) return rc;
+    for (int i = 0; i < m.num_layers; ++i) {
+      if (int rc = first_half(i, s)) return rc;
+      if (int rc = second_half(i, s)) return rc;
+    }
+    return head_and_pick(s);
   }
 };
 
@@ -488,6 +539,21 @@ int dfb_engine_step(void* engine, void* stream) {
     return DFB_ERR_ARG;
   }
   return ((Engine*)engine)->step((cudaStream_t)stream);
+}
+
+int dfb_engine_num_segments(void* engine) { return engine ? ((Engine*)engine)->num_segments() : 0; }
+
+int dfb_engine_step_segment(void* engine, int segment, void* stream) {
+  if (!engine) {
+    set_error("dfb_engine_step_segment: null engine");
+    return DFB_ERR_ARG;
+  }
+  return ((Engine*)engine)->step_segment(segment, (cudaStream_t)stream);
+}
+
+void* dfb_engine_partial_buffer(void* engine) {
+  Engine* e = (Engine*)engine;
+  return e && e->tp() ? (void*)e->at(e->ws.ar) : nullptr;
 }
 
 int dfb_engine_capture(void* engine, void* stream) {

@@ -113,6 +113,14 @@ __global__ void causal_conv_rows_kernel(bf16* x, long x_stride, bf16* cache, con
   st[2] = xv;
 }
 
+// Residual add of a projection whose fp32 partial sums were added across ranks: the sum is rounded to bf16
+// (what the unsharded projection would have returned), then added to the stream (src/deltaforge/reference.py:730,735).
+__global__ void add_partial_kernel(bf16* h, const float* sum, long n) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  h[i] = f2bf(__fadd_rn(bf2f(h[i]), round_bf16(sum[i])));
+}
+
 // Row gather of the embedding table (src/deltaforge/reference.py:804).
 __global__ void __launch_bounds__(128) embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out, float* ss_out,
                                                     int ss_count) {
@@ -253,6 +261,12 @@ int launch_causal_conv_rows(bf16* x, long x_stride, bf16* cache, const bf16* w, 
   if (total <= 0) return 0;
   causal_conv_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, x_stride, cache, w, channels, total);
   return check_launch("causal_conv_step (rows)");
+}
+
+int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  add_partial_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(h, sum, n);
+  return check_launch("add_partial");
 }
 
 int elementwise_configure() {

@@ -42,6 +42,10 @@ __device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
 
 // Output element (r, n) from its fp32 sum; returns the value stored (as fp32).
 __device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int n, float sum) {
+  if (p.epilogue == EPI_PARTIAL_F32) {
+    ((float*)p.out)[(long)r * p.out_stride + n] = sum;
+    return sum;
+  }
   bf16 y = f2bf(sum);
   if (p.epilogue == EPI_RESIDUAL) {
     float h = bf2f(p.residual[(long)r * p.res_stride + n]);

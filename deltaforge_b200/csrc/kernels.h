@@ -11,7 +11,8 @@ namespace dfb {
 typedef __nv_bfloat16 bf16;
 
 enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
-enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2 };
+// EPI_PARTIAL_F32 (engine-internal, tensor parallelism): `out` is an fp32 buffer that receives the unrounded sum
+enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2, EPI_PARTIAL_F32 = 3 };
 // MATH_FAST sums x*q per scale group and applies the fp32 scale once per group (the weight is
 // never rounded to bf16); MATH_EXACT rounds every dequantised weight to bf16 before the product,
 // as the reference's expression does.
@@ -209,6 +210,8 @@ int launch_argmax(const bf16* logits, int batch, int n, long stride, int64_t* ou
 // Opt the kernels with large dynamic shared memory in; call once before stream capture.
 int configure_kernels();
 int launch_advance(int* pos, int by, cudaStream_t s);
+// h <- bf16(h + bf16(sum)) over n elements: the residual add after an all-reduce of fp32 partial sums
+int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s);
 
 }  // namespace dfb
 

@@ -261,6 +261,7 @@ class DecodeEngine:
         attn_splits: int | None = None,
         math: int = MATH_FAST,
         persistent: bool = False,
+        tp_size: int = 1,
     ) -> None:
         """``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
         group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
@@ -329,6 +330,7 @@ class DecodeEngine:
         m.tokens, m.history, m.pos, m.logits = self.tokens.data_ptr(), self.history.data_ptr(), self.pos.data_ptr(), self.logits.data_ptr()
         m.attn_splits, m.math = self.attn_splits, math
         m.workspace, m.workspace_bytes = None, 0
+        m.tp_size = int(tp_size)
         m.persistent = int(persistent)
         self.persistent = bool(persistent)
         if persistent:

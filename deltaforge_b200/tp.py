@@ -1,0 +1,230 @@
+"""Tensor parallelism for the decode step: one process per GPU, every rank a shard of every layer.
+
+Sharding (the reference has no multi-GPU path; this follows its tensor shapes, src/deltaforge/reference.py:
+477-494, 592-605, 688-690): attention by query / KV head, DeltaNet by key / value head (value head ``h``
+uses key head ``h // (Hv / Hk)``, so a rank that owns a contiguous block of value heads owns the matching
+block of key heads), the MLP by intermediate channel, the tied head by vocabulary slice. Projections that
+produce per-head or per-channel outputs are sliced along N, which in the K-major int4 layout is a plain
+column slice of ``packed`` and ``scale``. The projections back to the hidden size (``out_proj`` / ``o_proj``,
+``down_proj``) are sliced along K on scale-group boundaries and re-packed, so every rank holds bit-identical
+int4 values and scales of its rows; each rank's product is a partial sum over its rows, the partial sums are
+added across ranks in fp32 (two all-reduces per layer), and the sum is rounded to bf16 and added to the
+residual stream exactly where the unsharded projection would have been. Norm weights, the embedding table
+and the residual stream are replicated. Greedy sampling compares each rank's best logit.
+
+The collective is NCCL through ``torch.distributed`` on the engine's stream, recorded with the kernels into
+one CUDA graph per token.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .config import LINEAR_ATTENTION
+from .engine import DecodeCache, DecodeEngine, LayerWeights, ModelWeights
+from .quant import QuantisedWeight, group_size_for
+
+BF16 = torch.bfloat16
+
+
+# --------------------------------------------------------------------------------------
+# sharding of shapes and weights (pure tensor code: runs on any device)
+# --------------------------------------------------------------------------------------
+
+
+def shard_config(cfg, tp: int):
+    """The model configuration one of ``tp`` ranks sees: its share of heads, MLP channels and vocabulary."""
+    for name in ("num_attention_heads", "num_key_value_heads", "linear_num_key_heads", "linear_num_value_heads",
+                 "intermediate_size", "vocab_size"):  # fmt: skip
+        if getattr(cfg, name) % tp:
+            raise ValueError(f"{name} = {getattr(cfg, name)} does not divide over {tp} ranks")
+    if (cfg.intermediate_size // tp) % 128 or (cfg.linear_num_value_heads // tp * cfg.linear_value_head_dim) % 128:
+        raise ValueError("K-sharded projections must keep whole 128-row scale groups on every rank")
+    return dataclasses.replace(
+        cfg,
+        num_attention_heads=cfg.num_attention_heads // tp,
+        num_key_value_heads=cfg.num_key_value_heads // tp,
+        linear_num_key_heads=cfg.linear_num_key_heads // tp,
+        linear_num_value_heads=cfg.linear_num_value_heads // tp,
+        intermediate_size=cfg.intermediate_size // tp,
+        vocab_size=cfg.vocab_size // tp,
+    )
+
+
+def unpack_k_major(packed: Tensor) -> Tensor:
+    """``packed [K/2, N]`` -> the stored nibbles ``[K, N]`` (still value + 8), uint8."""
+    return torch.cat([packed & 0xF, packed >> 4], dim=0)
+
+
+def pack_k_major(nibbles: Tensor) -> Tensor:
+    """Stored nibbles ``[K, N]`` -> ``packed [K/2, N]``: row ``j`` low, row ``j + K/2`` high."""
+    half = nibbles.shape[0] // 2
+    return (nibbles[:half] | (nibbles[half:] << 4)).contiguous()
+
+
+def slice_columns(qw: QuantisedWeight, cols: Tensor | slice) -> QuantisedWeight:
+    return QuantisedWeight(qw.qweight[:, cols].contiguous(), qw.scale[:, cols].contiguous(), qw.bits, qw.group_size)
+
+
+def slice_rows(qw: QuantisedWeight, k0: int, k1: int) -> QuantisedWeight:
+    """Rows ``[k0, k1)`` of the weight (whole scale groups), re-packed K-major: same nibbles, same scales."""
+    g = qw.group_size
+    if k0 % g or k1 % g:
+        raise ValueError(f"row slice [{k0}, {k1}) does not fall on {g}-row scale groups")
+    if group_size_for(k1 - k0) != g:
+        raise ValueError(f"a {k1 - k0}-row shard would not keep the group size {g}")
+    nib = unpack_k_major(qw.qweight)[k0:k1]
+    return QuantisedWeight(pack_k_major(nib), qw.scale[k0 // g : k1 // g].contiguous(), qw.bits, g)
+
+
+def _cat(parts: list[Tensor], device) -> Tensor:
+    return torch.cat([p.to(device) for p in parts])
+
+
+def shard_layer(lw: LayerWeights, cfg, rank: int, tp: int) -> LayerWeights:
+    dev = lw.in_proj.qweight.device
+    ar = lambda a, b: torch.arange(a, b, device=dev)  # noqa: E731
+    inter = cfg.intermediate_size
+    i0, i1 = rank * inter // tp, (rank + 1) * inter // tp
+    gate_up = slice_columns(lw.gate_up, _cat([ar(i0, i1), ar(inter + i0, inter + i1)], dev))
+    down = slice_rows(lw.down, i0, i1)
+    if lw.kind == LINEAR_ATTENTION:
+        hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        k0, k1 = rank * hk // tp, (rank + 1) * hk // tp
+        v0, v1 = rank * hv // tp, (rank + 1) * hv // tp
+        kd, vd = hk * dk, hv * dv
+        qkv = [ar(k0 * dk, k1 * dk), ar(kd + k0 * dk, kd + k1 * dk), ar(2 * kd + v0 * dv, 2 * kd + v1 * dv)]
+        cols = _cat(qkv + [ar(2 * kd + vd + v0 * dv, 2 * kd + vd + v1 * dv), ar(2 * kd + 2 * vd + v0, 2 * kd + 2 * vd + v1),
+                           ar(2 * kd + 2 * vd + hv + v0, 2 * kd + 2 * vd + hv + v1)], dev)  # fmt: skip
+        return LayerWeights(
+            kind=lw.kind, input_norm=lw.input_norm, post_norm=lw.post_norm,
+            in_proj=slice_columns(lw.in_proj, cols), out_proj=slice_rows(lw.out_proj, v0 * dv, v1 * dv), gate_up=gate_up, down=down,
+            conv_w=lw.conv_w[_cat(qkv, dev)].contiguous(), a_log=lw.a_log[v0:v1].contiguous(), dt_bias=lw.dt_bias[v0:v1].contiguous(),
+            gnorm_w=lw.gnorm_w, gnorm_w_is_bf16=lw.gnorm_w_is_bf16,
+        )  # fmt: skip
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    qw = 2 * d if cfg.attn_output_gate else d
+    q0, q1 = rank * hq // tp, (rank + 1) * hq // tp
+    g0, g1 = rank * hkv // tp, (rank + 1) * hkv // tp
+    cols = _cat([ar(q0 * qw, q1 * qw), ar(hq * qw + g0 * d, hq * qw + g1 * d), ar(hq * qw + hkv * d + g0 * d, hq * qw + hkv * d + g1 * d)], dev)
+    return LayerWeights(
+        kind=lw.kind, input_norm=lw.input_norm, post_norm=lw.post_norm,
+        in_proj=slice_columns(lw.in_proj, cols), out_proj=slice_rows(lw.out_proj, q0 * d, q1 * d), gate_up=gate_up, down=down,
+        q_norm=lw.q_norm, k_norm=lw.k_norm,
+    )  # fmt: skip
+
+
+def shard_weights(weights: ModelWeights, rank: int, tp: int) -> ModelWeights:
+    """Rank ``rank``'s shard of the model (``weights`` is the whole model, on any device)."""
+    cfg = weights.config
+    local = shard_config(cfg, tp)
+    v0, v1 = rank * cfg.vocab_size // tp, (rank + 1) * cfg.vocab_size // tp
+    out = ModelWeights(local, weights.embed, weights.final_norm, slice_columns(weights.head, slice(v0, v1)), weights.inv_freq)
+    out.layers = [shard_layer(lw, cfg, rank, tp) for lw in weights.layers]
+    return out
+
+
+def weights_to(weights: ModelWeights, device) -> ModelWeights:
+    """Move a (sharded) weight set to ``device``."""
+
+    def q(w: QuantisedWeight) -> QuantisedWeight:
+        return QuantisedWeight(w.qweight.to(device), w.scale.to(device), w.bits, w.group_size)
+
+    def t(x):
+        return None if x is None else x.to(device)
+
+    out = ModelWeights(weights.config, weights.embed.to(device), weights.final_norm.to(device), q(weights.head), weights.inv_freq.to(device))
+    for lw in weights.layers:
+        out.layers.append(
+            LayerWeights(
+                kind=lw.kind, input_norm=t(lw.input_norm), post_norm=t(lw.post_norm), in_proj=q(lw.in_proj), out_proj=q(lw.out_proj),
+                gate_up=q(lw.gate_up), down=q(lw.down), conv_w=t(lw.conv_w), a_log=t(lw.a_log), dt_bias=t(lw.dt_bias),
+                gnorm_w=t(lw.gnorm_w), gnorm_w_is_bf16=lw.gnorm_w_is_bf16, q_norm=t(lw.q_norm), k_norm=t(lw.k_norm),
+            )  # fmt: skip
+        )
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# the engine of one rank
+# --------------------------------------------------------------------------------------
+
+
+class TensorParallelEngine:
+    """One rank of a tensor-parallel decode step (batch 1..N, greedy).
+
+    ``local_weights`` / ``cache`` hold this rank's shard (``shard_weights``, ``DecodeCache(shard_config(cfg, tp), ...)``);
+    ``group`` is a ``torch.distributed`` process group whose backend can reduce CUDA tensors (NCCL).
+    """
+
+    def __init__(self, local_weights: ModelWeights, cache: DecodeCache, *, rank: int, tp: int, group=None) -> None:
+        import torch.distributed as dist
+
+        self.dist, self.group, self.rank, self.tp = dist, group, rank, tp
+        self.engine = DecodeEngine(local_weights, cache, tp_size=tp)
+        self.lib = self.engine.lib
+        self.cache = cache
+        dev = self.engine.device
+        self.vocab_local = local_weights.config.vocab_size
+        hidden = local_weights.config.hidden_size
+        ptr = self.lib.dfb_engine_partial_buffer(self.engine._handle)
+        off = ptr - self.engine.workspace.data_ptr()
+        n = self.engine.batch * hidden
+        self.partial = self.engine.workspace[off : off + 4 * n].view(torch.float32)  # the fp32 partial sums, in place
+        self.segments = self.lib.dfb_engine_num_segments(self.engine._handle)
+        self.best = torch.zeros((self.engine.batch, 2), dtype=torch.float32, device=dev)
+        self.gathered = torch.zeros((tp, self.engine.batch, 2), dtype=torch.float32, device=dev)
+        self._graph = None
+        self._warm = False
+
+    def _run(self) -> None:
+        stream = torch.cuda.current_stream(self.engine.device).cuda_stream
+        for seg in range(self.segments):
+            _lib.check(self.lib.dfb_engine_step_segment(self.engine._handle, seg, stream), "dfb_engine_step_segment")
+            if seg + 1 < self.segments:
+                self.dist.all_reduce(self.partial, group=self.group)
+        # greedy pick across the vocabulary shards: the largest logit wins, the lowest global index on ties
+        val, idx = self.engine.logits.float().max(dim=-1)
+        self.best[:, 0] = val
+        self.best[:, 1] = (idx + self.rank * self.vocab_local).float()  # exact: vocabulary sizes are far below 2^24
+        self.dist.all_gather_into_tensor(self.gathered.view(-1), self.best.view(-1), group=self.group)
+        vals, ids = self.gathered[..., 0], self.gathered[..., 1]
+        top = vals.max(dim=0, keepdim=True).values
+        masked = torch.where(vals == top, ids, torch.full_like(ids, float("inf")))
+        self.engine.tokens.copy_(masked.min(dim=0).values.long())
+
+    def step(self, tokens: Tensor, *, graph: bool = True) -> Tensor:
+        """One token for every sequence; returns this rank's slice of the logits ``[batch, vocab / tp]``.
+
+        The first call runs the kernels and collectives directly (that also sets NCCL's channels up); from the
+        second call on one CUDA graph per token is replayed."""
+        eng = self.engine
+        self.cache.ensure_capacity(1)
+        eng._sync_position()
+        eng._set_tokens(tokens)
+        if graph and self._warm:
+            if self._graph is None:
+                self._graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self._graph):  # recorded, not executed
+                    self._run()
+            self._graph.replay()
+        else:
+            self._run()
+            self._warm = True
+        self.cache.advance(1)
+        eng._pos_host += 1
+        return eng.logits
+
+    def decode(self, tokens: Tensor, steps: int) -> Tensor:
+        """Greedy loop on the device: returns the chosen tokens ``[batch, steps]`` (identical on every rank)."""
+        out = []
+        t = tokens
+        for _ in range(steps):
+            self.step(t)
+            t = self.engine.tokens.clone()
+            out.append(t)
+        return torch.stack(out, dim=1)

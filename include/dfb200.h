@@ -306,6 +306,12 @@ typedef struct dfb_model_desc {
   int32_t persistent;
   void* weight_stream;
   size_t weight_stream_bytes;
+  /* Tensor parallelism: > 1 says this engine holds one rank's shard (its heads, its slice of the MLP and of
+   * the vocabulary; all shapes above are the local ones). The projections that end each half of a layer are
+   * sharded along K: they leave fp32 partial sums [batch, hidden] in dfb_engine_partial_buffer() instead of
+   * adding into the residual stream, the caller adds that buffer across ranks (an all-reduce on the same
+   * stream) between dfb_engine_step_segment() calls, and picks the token across the vocabulary shards itself. */
+  int32_t tp_size;
 } dfb_model_desc;
 
 size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc);
@@ -318,6 +324,12 @@ int dfb_engine_create(const dfb_model_desc* desc, void** engine_out);
 int dfb_engine_destroy(void* engine);
 /* Enqueue the kernels of one step on `stream` (no graph). */
 int dfb_engine_step(void* engine, void* stream);
+/* Tensor-parallel engines: a step is dfb_engine_num_segments() = 2 * layers + 1 segments (embedding + first half
+ * of layer 0; second half of layer l; first half of layer l + 1; ...; LM head). Every segment but the first
+ * starts by adding the (all-reduced) partial buffer to the residual stream. */
+int dfb_engine_num_segments(void* engine);
+int dfb_engine_step_segment(void* engine, int segment, void* stream);
+void* dfb_engine_partial_buffer(void* engine);
 /* Capture one step into a CUDA graph (the position is read from device memory, so one graph serves
  * every token; the reference re-records per step, src/deltaforge/kernels/static_cache.py:62-74). */
 int dfb_engine_capture(void* engine, void* stream);

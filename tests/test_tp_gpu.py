@@ -1,0 +1,109 @@
+"""Tensor-parallel decode on two GPUs against the single-GPU engine on the same weights.
+
+Both ranks build the same seeded model; rank 0 also runs the unsharded engine; the tensor-parallel logits
+(gathered over the vocabulary shards) must match it within the noise of a different summation order, and
+the greedy tokens must agree on every rank. With two CUDA devices the ranks sit on one GPU each, reduce
+over NCCL and replay one CUDA graph per token; with a single device both ranks share it, reduce over gloo
+(through the host) and launch the segments directly: the kernels never wait on one another across ranks,
+the host does.
+"""
+
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _rank_main(rank: int, world: int, port: int, results, two_devices: bool):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank if two_devices else 0)
+    torch.cuda.set_device(dev)
+    if two_devices:
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    else:
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        from deltaforge_b200 import engine as E
+        from deltaforge_b200 import synth
+        from deltaforge_b200 import tp as TP
+        from deltaforge_b200.config import ModelConfig, hybrid_layer_types
+
+        cfg = ModelConfig(hidden_size=2560, intermediate_size=9216, num_hidden_layers=4, vocab_size=4096, layer_types=hybrid_layer_types(4))
+        full = synth.random_model_weights(cfg, seed=3, device=dev, scale_dtype=torch.bfloat16)
+        ctx_len, steps = 200, 4
+        # the whole model's cache, filled with seeded contents, and this rank's slice of it
+        whole_cache = E.DecodeCache(cfg, 1, 256, device=dev)
+        synth.fill_cache(whole_cache, ctx_len, seed=5)
+        local_cfg = TP.shard_config(cfg, world)
+        cache = E.DecodeCache(local_cfg, 1, 256, device=dev)
+        hk, hv, hkv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.num_key_value_heads
+        dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        for wl, ll in zip(whole_cache.layers, cache.layers):
+            wt, lt = E.cache_layer_tensors(wl), E.cache_layer_tensors(ll)
+            if "keys" in wt:
+                g0, g1 = rank * hkv // world, (rank + 1) * hkv // world
+                lt["keys"].copy_(wt["keys"][:, g0:g1])
+                lt["values"].copy_(wt["values"][:, g0:g1])
+            else:
+                k0, k1, v0, v1 = rank * hk // world, (rank + 1) * hk // world, rank * hv // world, (rank + 1) * hv // world
+                kd = hk * dk
+                rows = torch.cat([torch.arange(k0 * dk, k1 * dk), torch.arange(kd + k0 * dk, kd + k1 * dk),
+                                  torch.arange(2 * kd + v0 * dv, 2 * kd + v1 * dv)]).to(dev)  # fmt: skip
+                lt["conv"].copy_(wt["conv"][:, rows])
+                lt["recurrent"].copy_(wt["recurrent"][:, v0:v1])
+        cache.seq_len = ctx_len
+        eng = TP.TensorParallelEngine(TP.shard_weights(full, rank, world), cache, rank=rank, tp=world)
+        tok = torch.tensor([17], device=dev)
+        tp_logits, tp_tokens = [], []
+        t = tok
+        for _ in range(steps):  # first step direct, the rest through the captured graph
+            local = eng.step(t, graph=two_devices).clone()
+            gathered = [torch.zeros_like(local) for _ in range(world)]
+            dist.all_gather(gathered, local)
+            tp_logits.append(torch.cat(gathered, dim=-1))
+            t = eng.engine.tokens.clone()
+            tp_tokens.append(t)
+        ok = True
+        msg = ""
+        if rank == 0:
+            ref = E.DecodeEngine(full, whole_cache)
+            t = tok
+            for i in range(steps):
+                want = ref.step(t).clone()
+                scale = want.float().std().item()
+                err = (want.float() - tp_logits[i].float()).abs().max().item()
+                if not err < 6e-2 * scale:
+                    ok, msg = False, f"step {i}: max logit error {err:.4g} at scale {scale:.4g}"
+                t = tp_tokens[i]  # teacher-forced on the tensor-parallel continuation
+                if ok and int(want.argmax(-1)) != int(t) and (want.float().topk(2).values.diff().abs().item() > 2 * err):
+                    ok, msg = False, f"step {i}: token {int(t)} vs {int(want.argmax(-1))}"
+            ref.check_status()
+        eng.engine.check_status()
+        all_tok = [torch.zeros_like(tp_tokens[-1]) for _ in range(world)]
+        dist.all_gather(all_tok, tp_tokens[-1])
+        if rank == 0:
+            same = all(int(a) == int(all_tok[0]) for a in all_tok)
+            results.put((ok and same, msg or ("" if same else "ranks disagree on the token")))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_two_ranks_match_single_gpu():
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29700 + int(torch.randint(0, 200, (1,)).item())
+    two = torch.cuda.device_count() >= 2
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, results, two)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    ok, msg = results.get(timeout=10)
+    assert ok, msg
