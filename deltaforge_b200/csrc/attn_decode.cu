@@ -353,6 +353,7 @@ int launch_attn_decode(const AttnParams& p, cudaStream_t stream) {
     return 2;
   }
   const int groups = p.hq / p.hkv;
+  if (attn_mma_ok(p)) return launch_attn_decode_mma(p, nullptr, stream);
   if (p.d == 256 && (groups == 1 || groups == 2 || groups == 4 || groups == 8) && p.splits >= 1 &&
       p.splits <= MAX_SPLITS) {
     if (p.splits > 1 && (!p.part_acc || !p.part_ml || !p.counters)) {

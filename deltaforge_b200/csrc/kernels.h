@@ -140,6 +140,9 @@ struct AttnParams {
   long out_stride;
 };
 int launch_attn_decode(const AttnParams& p, cudaStream_t stream);
+// tensor-core (mma.sync) variant for many sequences or long caches; launch_attn_decode picks it when it applies
+bool attn_mma_ok(const AttnParams& p);
+int launch_attn_decode_mma(const AttnParams& p, int* status, cudaStream_t stream);
 
 struct AttnPrepParams {  // q/k RMSNorm + partial RoPE + KV-cache write for the new token
   int batch, hq, hkv, d, rotary_dim;

@@ -242,10 +242,11 @@ def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: i
         while splits * 2 * batch * kv_heads <= sm_count and max_seq_len // (splits * 2) >= 64:
             splits *= 2  # short caches: still use the SMs
         return splits
-    # longer caches take the two-kernel path, which has no slice limit
-    want = max(1, (2 * sm_count) // max(1, batch * kv_heads))
+    # longer caches take the two-kernel path, which has no slice limit: about eight waves of CTAs, slices of
+    # at least 256 keys (the tensor-core kernel streams 16-key tiles through a ring and wants a long slice)
+    want = max(1, (8 * sm_count) // max(1, batch * kv_heads))
     splits = 1
-    while splits * 2 <= min(want, 64) and max_seq_len // (splits * 2) >= 64:
+    while splits * 2 <= min(want, 128) and max_seq_len // (splits * 2) >= 256:
         splits *= 2
     return splits
 

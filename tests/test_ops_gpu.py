@@ -331,6 +331,31 @@ def test_attention_against_oracle(batch, hq, hkv, length, d, splits):
     close(got, want, rtol=2e-2, atol=2e-2)
 
 
+# many sequences or a long cache: the tensor-core kernel (16-key tiles through a ring, mma.sync)
+ATTN_MMA_CASES = [
+    (2, 16, 4, 1100, 1), (2, 16, 4, 1100, 8), (3, 8, 2, 4099, 8), (1, 16, 4, 20000, 64), (2, 8, 1, 700, 1),
+    (2, 4, 4, 300, 1), (2, 4, 2, 515, 2), (4, 16, 4, 129, 1),
+]  # fmt: skip
+
+
+@pytest.mark.parametrize("batch,hq,hkv,length,splits", ATTN_MMA_CASES)
+def test_attention_tensor_core_path_against_oracle(batch, hq, hkv, length, splits):
+    d = 256
+    q = torch.randn((batch, hq, d), generator=gen(610)).to(BF16)
+    k = torch.randn((batch, hkv, length, d), generator=gen(611)).to(BF16)
+    v = torch.randn((batch, hkv, length, d), generator=gen(612)).to(BF16)
+    scale = d**-0.5
+    truth = R.decode_attention_fp64(q, k, v, scale)
+    want = R.decode_attention(q, k, v, scale)
+    if splits == 1:
+        got = ops.gqa_decode_attention(q.to(DEV), k.to(DEV), v.to(DEV), scale)
+    else:
+        got = ops.split_kv_decode_attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, splits)
+    assert torch.isfinite(got.float()).all()
+    assert (got.cpu().double() - truth).abs().max().item() < 8e-3
+    close(got, want, rtol=2e-2, atol=2e-2)
+
+
 def test_attention_golden(golden):
     for case in golden("attention")["cases"]:
         got = ops.split_kv_decode_attention(case["q"].to(DEV), case["k"].to(DEV), case["v"].to(DEV), case["scale"], 8)
