@@ -10,10 +10,13 @@
 // and 32 for P.V, and the probabilities are rounded to bf16 before P.V as in the reference
 // (src/deltaforge/reference.py:660-672).
 //
-// Data path: one producer lane copies 16-key tiles (16 key rows + 16 value rows, 512 bytes each) with bulk
-// asynchronous copies into a 12-stage ring whose rows are padded to 528 bytes, so that the 8x8 matrix loads
-// (ldmatrix, transposed for V) are free of bank conflicts; tile t belongs to warp t mod 8, which frees the
-// stage itself. Waits are bounded and report through the status word.
+// Data path: one producer lane copies 16-key tiles with TMA (four 64-dim x 16-key boxes for the keys, four
+// for the values, 128-byte swizzle) into a 12-stage ring, so that the 8x8 matrix loads (ldmatrix, transposed
+// for V) are free of bank conflicts; tile t belongs to warp t mod 8, which frees the stage itself. (Copying
+// the 32 rows of a tile one by one caps an SM near 12 GB/s: the copy engine is bound by the number of
+// copies, not by their bytes.) Waits are bounded and report through the status word.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -24,8 +27,8 @@ namespace {
 constexpr int D = 256;
 constexpr int MW = 8;                          // compute warps
 constexpr int TK = 16;                         // keys per tile
-constexpr int ROWB = 528;                      // padded row: 512 bytes of bf16 + 16
-constexpr int TILEB = 2 * TK * ROWB;           // key rows, then value rows
+constexpr int BOXB = TK * 128;                 // one box: 16 keys x 64 dims of bf16, 128-byte swizzled
+constexpr int TILEB = 8 * BOXB;                // four key boxes, then four value boxes
 constexpr int MSTAGES = 12;
 constexpr int MMA_THREADS = (MW + 1) * 32;
 constexpr int MMA_MAX_SPLITS = 128;
@@ -56,12 +59,15 @@ __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatil
     }
   }
 }
-__device__ __forceinline__ void bulk_row(void* dst, const void* src, uint64_t* bar, uint64_t pol) {
+__device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int dim0, int key, int head, int seq, uint64_t* bar) {
   asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(smem_u32(dst)), "l"(src), "r"(D * 2), "r"(smem_u32(bar)), "l"(pol)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)map), "r"(dim0), "r"(key), "r"(head), "r"(seq), "r"(smem_u32(bar))
       : "memory");
 }
+// Byte offset of (row r, 16-byte chunk ch of the 512-byte row) inside a 4-box tile half: box ch / 8, 128-byte swizzle
+__device__ __forceinline__ uint32_t swz(int r, int ch) { return (uint32_t)((ch >> 3) * BOXB + r * 128 + (((ch & 7) ^ (r & 7)) << 4)); }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -80,8 +86,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 template <int GROUPS>
-__global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const AttnParams p, int* status) {
-  extern __shared__ __align__(128) unsigned char smraw[];
+__global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                         const __grid_constant__ CUtensorMap vmap, const AttnParams p,
+                                                                         int* status) {
+  extern __shared__ unsigned char smraw0[];
+  unsigned char* smraw = smraw0 + ((1024u - (smem_u32(smraw0) & 1023u)) & 1023u);  // swizzled boxes want 1024-byte alignment
   unsigned char* ring = smraw;                                   // [MSTAGES][TILEB]
   float* acc_s = (float*)smraw;                                  // [MW][GROUPS][D], reuses the ring after the scan
   float* ml_s = (float*)(smraw + (size_t)MSTAGES * TILEB);       // [MW][GROUPS][2]
@@ -119,18 +128,18 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const A
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = 0.f;
 
   if (warp == MW) {
-    // ---------------- producer ----------------
+    // ---------------- producer: eight boxes per tile ----------------
     if (lane == 0) {
-      const uint64_t pol = make_evict_first_policy();
       for (int tl = 0; tl < ntiles; ++tl) {
         const int s = tl % MSTAGES;
         if (tl >= MSTAGES && !mma_wait(&empty[s], ((tl / MSTAGES) - 1) & 1, failed)) break;
-        const int key0 = k_begin + tl * TK, n = min(TK, k_end - key0);
+        const int key0 = k_begin + tl * TK;
         unsigned char* st = ring + (size_t)s * TILEB;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full[s])), "r"(2 * n * D * 2) : "memory");
-        for (int r = 0; r < n; ++r) {
-          bulk_row(st + r * ROWB, kbase + (long)(key0 + r) * D, &full[s], pol);
-          bulk_row(st + (TK + r) * ROWB, vbase + (long)(key0 + r) * D, &full[s], pol);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full[s])), "r"(TILEB) : "memory");
+#pragma unroll
+        for (int bx = 0; bx < 4; ++bx) {
+          tma_box(st + bx * BOXB, &kmap, bx * 64, key0, hk, b, &full[s]);
+          tma_box(st + (4 + bx) * BOXB, &vmap, bx * 64, key0, hk, b, &full[s]);
         }
       }
     }
@@ -155,24 +164,19 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const A
       if (!mma_wait(&full[s], (tl / MSTAGES) & 1, failed)) break;
       unsigned char* st = ring + (size_t)s * TILEB;
       const int key0 = k_begin + tl * TK, n = min(TK, k_end - key0);
-      if (n < TK) {  // ragged last tile: rows that were not copied must not feed NaNs into the products
-        for (int i = lane; i < (TK - n) * (D * 2 / 16); i += 32) {
-          const int r = n + i / (D * 2 / 16), off = (i % (D * 2 / 16)) * 16;
-          *(uint4*)(st + r * ROWB + off) = make_uint4(0u, 0u, 0u, 0u);
-          *(uint4*)(st + (TK + r) * ROWB + off) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        __syncwarp();
-      }
+      // (rows of a ragged last tile past the live length are cache rows that were never written, or zero
+      // fill past the tensor: their scores are masked below and their value rows meet probability zero)
       // scores: S[16 x 16 keys] = Q[16 x 256] K^T, two n-tiles of 8 keys
       float sc[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-        const uint32_t kaddr = smem_u32(st + (nt * 8 + (lane & 7)) * ROWB + (lane >> 3) * 16);
+        const uint32_t kbase_s = smem_u32(st);
+        const int krow = nt * 8 + (lane & 7);
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) {
           uint32_t kb[4];  // dims 32kk + {0..7, 8..15, 16..23, 24..31} of the 8 keys
-          ldsm4(kaddr + kk * 64, kb);
+          ldsm4(kbase_s + swz(krow, 4 * kk + (lane >> 3)), kb);
           mma_bf16(sc[nt], qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, kb[0], kb[1]);
           mma_bf16(sc[nt], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, kb[2], kb[3]);
         }
@@ -196,11 +200,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const A
       mrun = mn;
       const uint32_t pa0 = pack2(pv[0], pv[1]), pa2 = pack2(pv[2], pv[3]);
       // O[16 x 256] = O * corr + P[16 x 16 keys] V[16 keys x 256]
-      const uint32_t vaddr = smem_u32(st + (TK + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROWB + (lane >> 4) * 16);
+      const uint32_t vbase_s = smem_u32(st + 4 * BOXB);
+      const int vrow = (lane & 7) + 8 * ((lane >> 3) & 1);
 #pragma unroll
       for (int j2 = 0; j2 < D / 16; ++j2) {
         uint32_t vb[4];  // (keys 0..7, dims 16j2..+7), (keys 8..15, same dims), (keys 0..7, dims +8..15), (keys 8..15, ...)
-        ldsm4_t(vaddr + j2 * 32, vb);
+        ldsm4_t(vbase_s + swz(vrow, 2 * j2 + (lane >> 4)), vb);
         float c0[4] = {o[2 * j2][0] * corr, o[2 * j2][1] * corr, z[0], z[1]};
         float c1[4] = {o[2 * j2 + 1][0] * corr, o[2 * j2 + 1][1] * corr, z[0], z[1]};
         mma_bf16(c0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
@@ -309,7 +314,34 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const A
 
 template <int GROUPS>
 size_t mma_smem() {
-  return (size_t)MSTAGES * TILEB + (size_t)(MW * GROUPS * 2 + GROUPS * MMA_MAX_SPLITS) * 4 + 2 * MSTAGES * 8 + 16;
+  return (size_t)MSTAGES * TILEB + (size_t)(MW * GROUPS * 2 + GROUPS * MMA_MAX_SPLITS) * 4 + 2 * MSTAGES * 8 + 16 + 1024;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn mma_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return (EncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+// The cache as a 4-D tensor [sequence][KV head][key][256] with the caller's strides; boxes are 64 dims x 16 keys.
+bool encode_cache_map(CUtensorMap* map, const bf16* base, const AttnParams& p) {
+  EncodeTiledFn enc = mma_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)p.key_len, (cuuint64_t)p.hkv, (cuuint64_t)p.batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)p.kv_head_stride * 2, (cuuint64_t)p.kv_batch_stride * 2};
+  const cuuint32_t box[4] = {64, TK, 1, 1};
+  const cuuint32_t es[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void*)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int GROUPS>
@@ -317,8 +349,13 @@ int launch_mma(const AttnParams& p, int* status, cudaStream_t stream) {
   static const cudaError_t once =
       cudaFuncSetAttribute(attn_decode_mma_kernel<GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem<GROUPS>());
   if (once != cudaSuccess) return check_launch("attention decode (tensor core): shared-memory opt-in");
-  if (launch_pdl(attn_decode_mma_kernel<GROUPS>, dim3(p.splits, p.hkv, p.batch), dim3(MMA_THREADS), mma_smem<GROUPS>(), stream, p,
-                 status) != cudaSuccess)
+  CUtensorMap kmap, vmap;
+  if (!encode_cache_map(&kmap, p.kcache, p) || !encode_cache_map(&vmap, p.vcache, p)) {
+    set_error("attention decode (tensor core): tensor map for the cache failed");
+    return 1;
+  }
+  if (launch_pdl(attn_decode_mma_kernel<GROUPS>, dim3(p.splits, p.hkv, p.batch), dim3(MMA_THREADS), mma_smem<GROUPS>(), stream, kmap, vmap,
+                 p, status) != cudaSuccess)
     return check_launch("attention decode (tensor core)");
   return check_launch("attention decode (tensor core)");
 }
@@ -331,7 +368,8 @@ bool attn_mma_ok(const AttnParams& p) {
   const int cap = p.key_len;  // live length, or the cache capacity when the position is on the device
   return p.d == D && (groups == 1 || groups == 2 || groups == 4 || groups == 8) && p.splits >= 1 && p.splits <= MMA_MAX_SPLITS &&
          (p.splits == 1 || (p.part_acc && p.part_ml && p.counters)) && cap / p.splits >= 128 && (p.batch >= 2 || cap >= 16384) &&
-         ((uintptr_t)p.kcache % 16) == 0 && ((uintptr_t)p.vcache % 16) == 0 && p.kv_batch_stride % 8 == 0 && p.kv_head_stride % 8 == 0;
+         ((uintptr_t)p.kcache % 16) == 0 && ((uintptr_t)p.vcache % 16) == 0 && p.kv_batch_stride % 8 == 0 && p.kv_head_stride % 8 == 0 &&
+         mma_encode_fn() != nullptr;
 }
 
 int launch_attn_decode_mma(const AttnParams& p, int* status, cudaStream_t stream) {
