@@ -224,7 +224,10 @@ struct Engine {
   int mixer_attention(const dfb_layer_desc& L, bf16* proj, long pstride, bf16* mix, bf16* qout, cudaStream_t s) {
     const int d_ = m.head_dim;
     const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
-    if (attn_step_ok(d_, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) {
+    // One or two sequences: the fused single-launch kernel (latency matters). More: its 160-key staging leaves
+    // one CTA per SM alternating between copying and computing, and the two-kernel path with the tensor-core
+    // decode streams the cache several times faster.
+    if (m.batch <= 2 && attn_step_ok(d_, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) {
       // norms, RoPE, KV write, split-KV decode, merge and gate in one launch
       AttnStepParams q = {};
       q.batch = m.batch;

@@ -238,7 +238,7 @@ def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: i
     splits = 1
     while splits < 128 and -(-max_seq_len // splits) > 160:
         splits *= 2
-    if -(-max_seq_len // splits) <= 160:
+    if batch <= 2 and -(-max_seq_len // splits) <= 160:
         while splits * 2 * batch * kv_heads <= sm_count and max_seq_len // (splits * 2) >= 64:
             splits *= 2  # short caches: still use the SMs
         return splits
