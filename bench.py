@@ -256,11 +256,16 @@ def time_head_gemv(weights, iters: int = 30) -> tuple[float, int]:
     for _ in range(5):
         call()
     torch.cuda.synchronize()
-    # `iters` launches recorded into one CUDA graph, so that the host's per-call cost is outside the timed region
+    # `iters` launches recorded into one CUDA graph, so that the host's per-call cost is outside the timed region.
+    # A one-element torch kernel between them keeps consecutive launches from overlapping through programmatic
+    # dependent launch (in the decode step the head runs once per token, after other kernels); its microsecond
+    # is counted against the GEMV.
+    tick = torch.zeros(1, device=x.device)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         for _ in range(iters):
             call()
+            tick.add_(1.0)
     graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

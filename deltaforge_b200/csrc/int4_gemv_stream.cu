@@ -231,9 +231,13 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
   int tile_first_rb = -1;
   bool ok = true;
 
-  for (int u = u0, it = 0; u < u1; ++u, ++it) {
-    const int s = it % a.stages;
-    const int tile = u / a.rbc, rb = u % a.rbc;
+  // (tile, rb) of the unit, the ring stage and its phase advance by increments: no division in the loop
+  int tile = u0 / a.rbc, rb = u0 % a.rbc, s = 0, phase = 0;
+  auto advance = [&]() {
+    if (++rb == a.rbc) rb = 0, ++tile;
+    if (++s == a.stages) s = 0, phase ^= 1;
+  };
+  for (int u = u0; u < u1; ++u, advance()) {
     const int kb0 = rb * RBK, g = kb0 >> 4;
     const int ncol = tile * TNW + n0;
     if (tile_first_rb < 0) tile_first_rb = rb;
@@ -250,7 +254,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
         }
       }
     }
-    ok = mbar_wait(&full[s], (it / a.stages) & 1);
+    ok = mbar_wait(&full[s], phase);
     if (!ok) break;
     const unsigned char* wbase = ring + (size_t)s * STAGE + box_off;
 #pragma unroll
@@ -271,7 +275,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);
 
-    const bool tile_done = (u + 1 == u1) || ((u + 1) / a.rbc != tile);
+    const bool tile_done = (u + 1 == u1) || (rb + 1 == a.rbc);
     const bool group_done = tile_done || (((kb0 + RBK) & 15) == 0);
     if (group_done) {
       const float f = fg[g];
