@@ -433,13 +433,13 @@ def run_tp(args) -> dict | None:
     synth.fill_cache(cache, CONTEXT, seed=77)
     eng = TP.TensorParallelEngine(shard, cache, rank=rank, tp=world)
     tok = torch.full((BATCH,), 1000, dtype=torch.int64, device=dev)
-    eng.decode(tok, warmup)
+    eng.decode(tok, warmup, graph=args.tp_graph)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local) as clocks:
         e0.record()
-        eng.decode(tok, steps)
+        eng.decode(tok, steps, graph=args.tp_graph)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
@@ -469,6 +469,7 @@ def run_tp(args) -> dict | None:
             "workload": f"qwen3.5-4b int4 decode step, batch {BATCH}, ctx {CONTEXT}, ONE replica tensor-parallel over {world} GPUs",
             "parallelism": f"tp{world}: heads, MLP channels and vocabulary sharded; two fp32 all-reduces (NCCL) per layer",
             "all_reduces_per_token": 2 * cfg.num_hidden_layers,
+            "launch": "one CUDA graph per token" if args.tp_graph else "segments and collectives launched directly",
         },
         "clocks": clocks.summary(),
         "roofline_step": {"bytes_per_token": bytes_step["total"], "achieved": bytes_step["total"] / (ms_max / steps * 1e-3) / 1e9,
@@ -493,6 +494,7 @@ def main() -> None:
         "the line it prints is marked and is not a bench value",
     )
     ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
+    ap.add_argument("--tp-graph", action="store_true", help="with --tp: record kernels and collectives into one CUDA graph per token")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 1: the metric's configuration)")
     ap.add_argument("--context", type=int, default=None, help="tokens already in the cache (default 4096)")
     args = ap.parse_args()

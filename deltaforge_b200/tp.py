@@ -12,8 +12,8 @@ added across ranks in fp32 (two all-reduces per layer), and the sum is rounded t
 residual stream exactly where the unsharded projection would have been. Norm weights, the embedding table
 and the residual stream are replicated. Greedy sampling compares each rank's best logit.
 
-The collective is NCCL through ``torch.distributed`` on the engine's stream, recorded with the kernels into
-one CUDA graph per token.
+The collective is NCCL through ``torch.distributed`` on the engine's stream; kernels and collectives can be
+recorded into one CUDA graph per token (``graph=True``).
 """
 
 from __future__ import annotations
@@ -197,11 +197,12 @@ class TensorParallelEngine:
         masked = torch.where(vals == top, ids, torch.full_like(ids, float("inf")))
         self.engine.tokens.copy_(masked.min(dim=0).values.long())
 
-    def step(self, tokens: Tensor, *, graph: bool = True) -> Tensor:
+    def step(self, tokens: Tensor, *, graph: bool = False) -> Tensor:
         """One token for every sequence; returns this rank's slice of the logits ``[batch, vocab / tp]``.
 
-        The first call runs the kernels and collectives directly (that also sets NCCL's channels up); from the
-        second call on one CUDA graph per token is replayed."""
+        By default the segments and the collectives between them are launched directly. With ``graph=True`` the
+        first call still runs directly (that also sets NCCL's channels up) and from the second call on one CUDA
+        graph per token, collectives included, is replayed."""
         eng = self.engine
         self.cache.ensure_capacity(1)
         eng._sync_position()
@@ -219,12 +220,12 @@ class TensorParallelEngine:
         eng._pos_host += 1
         return eng.logits
 
-    def decode(self, tokens: Tensor, steps: int) -> Tensor:
+    def decode(self, tokens: Tensor, steps: int, *, graph: bool = False) -> Tensor:
         """Greedy loop on the device: returns the chosen tokens ``[batch, steps]`` (identical on every rank)."""
         out = []
         t = tokens
         for _ in range(steps):
-            self.step(t)
+            self.step(t, graph=graph)
             t = self.engine.tokens.clone()
             out.append(t)
         return torch.stack(out, dim=1)

@@ -2,10 +2,9 @@
 
 Both ranks build the same seeded model; rank 0 also runs the unsharded engine; the tensor-parallel logits
 (gathered over the vocabulary shards) must match it within the noise of a different summation order, and
-the greedy tokens must agree on every rank. With two CUDA devices the ranks sit on one GPU each, reduce
-over NCCL and replay one CUDA graph per token; with a single device both ranks share it, reduce over gloo
-(through the host) and launch the segments directly: the kernels never wait on one another across ranks,
-the host does.
+the greedy tokens must agree on every rank. With two CUDA devices the ranks sit on one GPU each and reduce
+over NCCL; with a single device both ranks share it and reduce over gloo (through the host). The segments
+are launched directly in both cases: the kernels never wait on one another across ranks, the host does.
 """
 
 from __future__ import annotations
@@ -63,7 +62,7 @@ def _rank_main(rank: int, world: int, port: int, results, two_devices: bool):
         tp_logits, tp_tokens = [], []
         t = tok
         for _ in range(steps):  # first step direct, the rest through the captured graph
-            local = eng.step(t, graph=two_devices).clone()
+            local = eng.step(t).clone()  # segments and collectives launched directly
             gathered = [torch.zeros_like(local) for _ in range(world)]
             dist.all_gather(gathered, local)
             tp_logits.append(torch.cat(gathered, dim=-1))
@@ -103,7 +102,12 @@ def test_tensor_parallel_two_ranks_match_single_gpu():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(600)
-        assert p.exitcode == 0
+        p.join(150)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:  # a rank that never finished: end exactly the processes this test started
+        p.kill()
+        p.join(10)
+    assert not hung, "a rank did not finish within 150 s"
+    assert all(p.exitcode == 0 for p in procs)
     ok, msg = results.get(timeout=10)
     assert ok, msg
