@@ -158,6 +158,128 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   }
 }
 
+// Many sequences: one CTA owns a whole value head (all dv <= 128 columns, 64 state values per thread), so the
+// head's sum of squares stays inside the CTA and the grid needs no clusters: with 32 sequences the clustered
+// kernel above launches 1024 clusters of four small CTAs per layer and spends most of its time scheduling them.
+constexpr int HB_COLS = 4;  // column groups of 32 per thread: dv <= 128
+__global__ void __launch_bounds__(DN_WARPS * 32, 2) deltanet_head_kernel(const DeltaNetParams p) {
+  __shared__ float qn[MAX_DK], kn[MAX_DK];
+  __shared__ float red[2 * DN_WARPS * HB_COLS * VB];
+  __shared__ float wred[DN_WARPS];
+  __shared__ float gates[2];
+  const int hv = blockIdx.x, b = blockIdx.y;
+  const int hk = hv / (p.num_v_heads / p.num_k_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  const int dk = p.dk, dv = p.dv;
+  pdl_launch_dependents();
+  // the state of the head goes in flight first; nothing below depends on it until the recurrence
+  float* S = p.state + ((long)(b * p.num_v_heads + hv) * dk) * dv;
+  float s[HB_COLS][RPT];
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int k = warp * RPT + i, col = c * VB + lane;
+      s[c][i] = (col < dv && k < dk) ? __ldcs(S + (long)k * dv + col) : 0.f;
+    }
+  pdl_wait();
+  const long row = (long)b * p.row_stride;
+  {
+    const bool is_k = t >= MAX_DK;
+    const int j = is_k ? t - MAX_DK : t;
+    float x = 0.f;
+    if (j < dk) x = bf2f((is_k ? p.k : p.q)[row + (long)hk * dk + j]);
+    const float ss = warp_sum(x * x);
+    if (lane == 0) wred[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    const int w0 = is_k ? DN_WARPS / 2 : 0;
+#pragma unroll
+    for (int w = 0; w < DN_WARPS / 2; ++w) tot += wred[w0 + w];
+    float xn = __fmul_rn(x, rsqrt_2step(__fadd_rn(tot, 1e-6f)));
+    if (!is_k) xn = __fdiv_rn(xn, sqrtf((float)dk));
+    if (j < dk) (is_k ? kn : qn)[j] = xn;
+    if (t == 0) {
+      const float beta = round_bf16(sigmoid_f(bf2f(p.b[row + hv])));
+      const float g = __fmul_rn(-expf(p.a_log[hv]), softplus_f(__fadd_rn(bf2f(p.a[row + hv]), p.dt_bias[hv])));
+      gates[0] = beta;
+      gates[1] = expf(g);
+    }
+  }
+  float vval[HB_COLS], zval[HB_COLS];
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c) {
+    const int col = c * VB + lane;
+    vval[c] = col < dv ? bf2f(p.v[row + (long)hv * dv + col]) : 0.f;
+    zval[c] = col < dv ? bf2f(p.z[row + (long)hv * dv + col]) : 0.f;
+  }
+  __syncthreads();
+  const float decay = gates[1], beta = gates[0];
+  // r = S^T k on the decayed state, all four column groups in one pass and one barrier
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c) {
+    float r = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int k = warp * RPT + i;
+      s[c][i] = __fmul_rn(s[c][i], decay);
+      if (k < dk) r = fmaf(s[c][i], kn[k], r);
+    }
+    red[(warp * HB_COLS + c) * VB + lane] = r;
+  }
+  __syncthreads();
+  float o[HB_COLS];
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c) {
+    float r = 0.f;
+#pragma unroll
+    for (int w = 0; w < DN_WARPS; ++w) r += red[(w * HB_COLS + c) * VB + lane];
+    const float delta = __fmul_rn(__fsub_rn(vval[c], r), beta);
+    float oc = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int k = warp * RPT + i;
+      if (k < dk) {
+        s[c][i] = __fadd_rn(s[c][i], __fmul_rn(kn[k], delta));
+        oc = fmaf(s[c][i], qn[k], oc);
+      }
+    }
+    red[((DN_WARPS + warp) * HB_COLS + c) * VB + lane] = oc;
+  }
+  __syncthreads();
+  // the updated state goes straight back
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c)
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int k = warp * RPT + i, col = c * VB + lane;
+      if (col < dv && k < dk) __stcs(S + (long)k * dv + col, s[c][i]);
+    }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c) {
+    float oc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DN_WARPS; ++w) oc += red[((DN_WARPS + w) * HB_COLS + c) * VB + lane];
+    o[c] = (c * VB + lane) < dv ? round_bf16(oc) : 0.f;
+    ss = fmaf(o[c], o[c], ss);
+  }
+  if (warp != 0) return;
+  // gated RMSNorm over the head's dv outputs (src/deltaforge/reference.py:115-121): every warp holds all of them
+  const float tot = warp_sum(ss);
+  const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)dv), p.eps));
+#pragma unroll
+  for (int c = 0; c < HB_COLS; ++c) {
+    const int col = c * VB + lane;
+    if (col >= dv) continue;
+    const float nrm = round_bf16(__fmul_rn(o[c], rstd));
+    float y = __fmul_rn(p.norm_w[col], nrm);
+    if (p.norm_w_bf16) y = round_bf16(y);
+    y = __fmul_rn(y, silu_f(zval[c]));
+    p.out[(long)b * p.out_stride + (long)hv * dv + col] = f2bf(y);
+  }
+}
+
 // The bare recurrence with the reference op's contract (src/deltaforge/kernels/gated_delta_step.py:
 // 109-177): q, k already normalised, everything fp32, new state written to a separate tensor.
 __global__ void __launch_bounds__(DN_WARPS * 32) delta_rule_kernel(const DeltaRuleParams p) {
@@ -194,6 +316,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) delta_rule_kernel(const DeltaRu
 
 int deltanet_configure() {
   cudaError_t e = prefer_max_shared(deltanet_fused_kernel);
+  if (e == cudaSuccess) e = prefer_max_shared(deltanet_head_kernel);
   if (e == cudaSuccess) e = prefer_max_shared(delta_rule_kernel);
   return e == cudaSuccess ? 0 : check_launch("deltanet step: shared-memory carve-out");
 }
@@ -207,6 +330,11 @@ int launch_deltanet_step(const DeltaNetParams& p, cudaStream_t stream) {
   if (p.num_k_heads < 1 || p.num_v_heads % p.num_k_heads) {
     set_error("deltanet step: %d value heads do not divide into %d key heads", p.num_v_heads, p.num_k_heads);
     return 2;
+  }
+  if (p.batch >= 4 && p.dv <= HB_COLS * VB) {  // many sequences: a CTA per (head, sequence), no clusters
+    if (launch_pdl(deltanet_head_kernel, dim3(p.num_v_heads, p.batch), dim3(DN_WARPS * 32), 0, stream, p) != cudaSuccess)
+      return check_launch("deltanet step (per head)");
+    return check_launch("deltanet step (per head)");
   }
   const int nvb = (p.dv + VB - 1) / VB;
   cudaLaunchConfig_t cfg = {};

@@ -282,7 +282,14 @@ def test_delta_rule_rejects_bf16_state():
         ops.delta_rule_step(z((1, 1, 4, 4), dtype=BF16), z((1, 1, 4)), z((1, 1, 4)), z((1, 1, 4)), z((1, 1)), z((1, 1)))
 
 
-@pytest.mark.parametrize("batch,hk,hv,dk,dv,wdtype", [(1, 16, 32, 128, 128, BF16), (2, 2, 4, 16, 16, BF16), (1, 16, 32, 128, 128, torch.float32)])
+@pytest.mark.parametrize(
+    "batch,hk,hv,dk,dv,wdtype",
+    [
+        (1, 16, 32, 128, 128, BF16), (2, 2, 4, 16, 16, BF16), (1, 16, 32, 128, 128, torch.float32),
+        # four sequences and more: the one-CTA-per-head kernel
+        (4, 16, 32, 128, 128, BF16), (5, 2, 4, 16, 16, BF16), (4, 4, 8, 64, 96, torch.float32),
+    ],
+)  # fmt: skip
 def test_deltanet_step_against_oracle(batch, hk, hv, dk, dv, wdtype):
     q = torch.randn((batch, hk, dk), generator=gen(500)).to(BF16)
     k = torch.randn((batch, hk, dk), generator=gen(501)).to(BF16)
