@@ -431,7 +431,7 @@ def run_tp(args) -> dict | None:
     torch.cuda.empty_cache()
     cache = E.DecodeCache(TP.shard_config(cfg, world), BATCH, CONTEXT + steps + warmup + 8, device=dev)
     synth.fill_cache(cache, CONTEXT, seed=77)
-    eng = TP.TensorParallelEngine(shard, cache, rank=rank, tp=world)
+    eng = TP.TensorParallelEngine(shard, cache, rank=rank, tp=world, exchange=args.tp_exchange)
     tok = torch.full((BATCH,), 1000, dtype=torch.int64, device=dev)
     eng.decode(tok, warmup, graph=args.tp_graph)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -467,9 +467,10 @@ def run_tp(args) -> dict | None:
         "data": "synthetic",
         "config": {
             "workload": f"qwen3.5-4b int4 decode step, batch {BATCH}, ctx {CONTEXT}, ONE replica tensor-parallel over {world} GPUs",
-            "parallelism": f"tp{world}: heads, MLP channels and vocabulary sharded; two fp32 all-reduces (NCCL) per layer",
+            "parallelism": f"tp{world}: heads, MLP channels and vocabulary sharded; two fp32 all-reduces per layer",
             "all_reduces_per_token": 2 * cfg.num_hidden_layers,
-            "launch": "one CUDA graph per token" if args.tp_graph else "segments and collectives launched directly",
+            "exchange": "peer stores inside the kernels (no collective call)" if args.tp_exchange == "peer" else "NCCL all-reduce",
+            "launch": "one CUDA graph per token" if (args.tp_graph or args.tp_exchange == "peer") else "segments and collectives launched directly",
         },
         "clocks": clocks.summary(),
         "roofline_step": {"bytes_per_token": bytes_step["total"], "achieved": bytes_step["total"] / (ms_max / steps * 1e-3) / 1e9,
@@ -494,6 +495,7 @@ def main() -> None:
         "the line it prints is marked and is not a bench value",
     )
     ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
+    ap.add_argument("--tp-exchange", choices=("nccl", "peer"), default="nccl", help="with --tp: how the ranks add their partial sums")
     ap.add_argument("--tp-graph", action="store_true", help="with --tp: record kernels and collectives into one CUDA graph per token")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 1: the metric's configuration)")
     ap.add_argument("--context", type=int, default=None, help="tokens already in the cache (default 4096)")

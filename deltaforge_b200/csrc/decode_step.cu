@@ -37,7 +37,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, ar, pstep, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, ar, epoch, pstep, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -83,6 +83,7 @@ Workspace plan(const dfb_model_desc& m) {
   // batches of eight and more: the normalised / gated activation the tensor-core product reads
   w.xn = take(m.batch >= 8 ? B * std::max(std::max((size_t)m.hidden, (size_t)m.intermediate), mixw) * 2 : 0);
   w.ar = take(m.tp_size > 1 ? B * m.hidden * 4 : 0);
+  w.epoch = take(m.tp_size > 1 ? 256 : 0);
   w.pstep = take(m.persistent ? pstep_workspace_bytes(m) : 0);
   w.total = off;
   return w;
@@ -97,12 +98,14 @@ struct Engine {
   int launches = 0;
   bool ss_valid = false;  // the residual stream's per-tile sums of squares in h_ss are current
   PStep* ps = nullptr;    // the persistent-kernel form of the step, when the model asked for it
+  unsigned long long* peer_slots[TP_MAX] = {};  // tensor parallelism by peer stores: every rank's exchange buffer
+  TpPeer cur_peer = {};                          // where the next EPI_PARTIAL_PEER projection writes
 
   char* at(size_t off) const { return (char*)m.workspace + off; }
 
   int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
            long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
-    if (m.batch >= 8 && l.packed_k8 && m.math != MATH_FAST_HALF2 && epilogue != EPI_PARTIAL_F32) {
+    if (m.batch >= 8 && l.packed_k8 && m.math != MATH_FAST_HALF2 && epilogue != EPI_PARTIAL_F32 && epilogue != EPI_PARTIAL_PEER) {
       // Tensor-core path: prologue and the conv epilogue run as their own small kernels around the product.
       GemvParams q = {};
       q.x = x;
@@ -179,6 +182,7 @@ struct Engine {
     p.counters = (unsigned*)at(ws.counters);
     p.math = m.math;
     p.status = (int*)at(ws.status);
+    if (epilogue == EPI_PARTIAL_PEER) p.peer = cur_peer;
     // Sum-of-squares hand-off along the residual stream (batch 1, cluster kernel on both sides).
     const int h_tiles = (m.hidden + cluster_tile_width(m.hidden) - 1) / cluster_tile_width(m.hidden);
     if (prologue == PRO_RMSNORM && x_is_h && ss_valid) {
@@ -329,6 +333,17 @@ struct Engine {
   // sums in the `ar` buffer instead of adding into the residual stream; the caller all-reduces that buffer
   // between segments and the next segment starts with the residual add.
   bool tp() const { return m.tp_size > 1; }
+  bool peer() const { return tp() && peer_slots[0] != nullptr; }
+  long bh() const { return (long)m.batch * m.hidden; }
+  // all-reduce number `a` of the step (0 .. 2 * layers - 1) alternates between two slot sets
+  void aim_peer(int a) {
+    cur_peer = {};
+    for (int r = 0; r < m.tp_size; ++r) cur_peer.slots[r] = peer_slots[r];
+    cur_peer.tp_size = m.tp_size;
+    cur_peer.epoch_ctr = (const unsigned*)at(ws.epoch);
+    cur_peer.epoch_off = a;
+    cur_peer.word_off = ((long)(a & 1) * m.tp_size + m.tp_rank) * bh();
+  }
   int num_segments() const { return tp() ? 2 * m.num_layers + 1 : 1; }
 
   int first_half(int i, cudaStream_t s) {  // input projections, token mixer, output projection
@@ -344,6 +359,10 @@ struct Engine {
     rc = dn ? mixer_deltanet(L, proj, pstride, mix, s) : mixer_attention(L, proj, pstride, mix, (bf16*)at(ws.qout), s);
     if (rc) return rc;
     const long mixw = dn ? (long)m.lin_v_heads * m.lin_dv : (long)m.hq * m.head_dim;
+    if (peer()) {
+      aim_peer(2 * i);
+      return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_PARTIAL_PEER, (bf16*)at(ws.ar), H, nullptr, s);
+    }
     if (tp()) return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
     return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
   }
@@ -355,6 +374,10 @@ struct Engine {
     const int H = m.hidden, I = m.intermediate;
     int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
     if (rc) return rc;
+    if (peer()) {
+      aim_peer(2 * i + 1);
+      return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_PARTIAL_PEER, (bf16*)at(ws.ar), H, nullptr, s);
+    }
     if (tp()) return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
     return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
   }
@@ -363,6 +386,28 @@ struct Engine {
     bf16* h = (bf16*)at(ws.h);
     int rc = gemv(m.head, h, m.hidden, PRO_RMSNORM, m.final_norm_w, nullptr, 0, EPI_STORE, (bf16*)m.logits, m.vocab, nullptr, s);
     if (rc) return rc;
+    if (peer()) {
+      // each rank's best logit, then the pick across the vocabulary shards by peer exchange
+      rc = launch_argmax((const bf16*)m.logits, m.batch, m.vocab, m.vocab, m.tokens, nullptr, m.pos, (float*)at(ws.am_val),
+                         (int*)at(ws.am_idx), (unsigned*)at(ws.am_ctr), s);
+      ++launches;
+      if (rc) return rc;
+      TpPeer pk = {};
+      for (int r = 0; r < m.tp_size; ++r) pk.slots[r] = peer_slots[r];
+      pk.tp_size = m.tp_size;
+      pk.epoch_ctr = (const unsigned*)at(ws.epoch);
+      pk.epoch_off = 255;
+      pk.word_off = 2L * m.tp_size * bh();
+      rc = launch_tp_pick((const bf16*)m.logits, m.vocab, m.batch, m.tp_rank, pk, peer_slots[m.tp_rank], m.tokens, m.history, m.pos,
+                          (int*)at(ws.status), s);
+      ++launches;
+      if (rc) return rc;
+      rc = launch_advance(m.pos, 1, s);
+      ++launches;
+      if (rc) return rc;
+      ++launches;
+      return launch_bump((unsigned*)at(ws.epoch), s);
+    }
     if (!tp()) {  // with a sharded vocabulary the caller picks the token across ranks
       rc = launch_argmax((const bf16*)m.logits, m.batch, m.vocab, m.vocab, m.tokens, m.history, m.pos, (float*)at(ws.am_val),
                          (int*)at(ws.am_idx), (unsigned*)at(ws.am_ctr), s);
@@ -382,9 +427,14 @@ struct Engine {
     return launch_embed((const bf16*)m.embed, m.tokens, m.batch, H, (bf16*)at(ws.h), ss_valid ? (float*)at(ws.h_ss) : nullptr, h_tiles, s);
   }
 
-  int add_partial(cudaStream_t s) {
+  int add_partial(int seg, cudaStream_t s) {
     ss_valid = false;
     ++launches;
+    if (peer()) {
+      const int a = seg - 1;  // the all-reduce that ended the previous segment
+      return launch_tp_reduce((bf16*)at(ws.h), peer_slots[m.tp_rank], m.tp_size, bh(), (long)(a & 1) * m.tp_size * bh(),
+                              (const unsigned*)at(ws.epoch), a, (int*)at(ws.status), s);
+    }
     return launch_add_partial((bf16*)at(ws.h), (const float*)at(ws.ar), (long)m.batch * m.hidden, s);
   }
 
@@ -400,7 +450,7 @@ struct Engine {
     if (seg == 0) {
       if (int rc = embed(s)) return rc;
     } else {
-      if (int rc = add_partial(s)) return rc;
+      if (int rc = add_partial(seg, s)) return rc;
     }
     if (seg == 2 * m.num_layers) return head_and_pick(s);
     if (seg & 1) return second_half(seg / 2, s);
@@ -411,6 +461,11 @@ struct Engine {
     if (ps) {
       launches = 1;
       return pstep_launch(ps, s);
+    }
+    if (peer()) {  // the ranks exchange by peer stores inside the kernels: the whole step is one launch sequence
+      for (int seg = 0; seg < num_segments(); ++seg)
+        if (int rc = step_segment(seg, s)) return rc;
+      return 0;
     }
     if (tp()) {
       set_error("engine: a tensor-parallel step is run segment by segment, with an all-reduce of the partial buffer in between");
@@ -514,6 +569,28 @@ int dfb_engine_create(const dfb_model_desc* desc, void** engine_out) {
   e->layers.assign(desc->layers_host, desc->layers_host + desc->num_layers);
   e->m.layers_host = e->layers.data();
   e->ws = w;
+  if (desc->tp_size > 1) {
+    if (desc->tp_size > TP_MAX || desc->tp_rank < 0 || desc->tp_rank >= desc->tp_size) {
+      set_error("engine: tensor-parallel rank %d of %d (at most %d ranks)", desc->tp_rank, desc->tp_size, TP_MAX);
+      delete e;
+      return DFB_ERR_ARG;
+    }
+    const unsigned one = 1;
+    if (cudaMemcpy(e->at(w.epoch), &one, sizeof(one), cudaMemcpyHostToDevice) != cudaSuccess) {
+      delete e;
+      return check_launch("engine: epoch counter");
+    }
+    if (desc->tp_peer_slots)
+      for (int r = 0; r < desc->tp_size; ++r) {
+        e->peer_slots[r] = (unsigned long long*)desc->tp_peer_slots[r];
+        if (!e->peer_slots[r] || ((uintptr_t)e->peer_slots[r] % 8) != 0) {
+          set_error("engine: exchange buffer of rank %d is null or misaligned", r);
+          delete e;
+          return DFB_ERR_ARG;
+        }
+      }
+    e->m.tp_peer_slots = nullptr;  // copied; the caller's array need not outlive creation
+  }
   if (desc->persistent) {
     const int rc = pstep_create(e->m, e->at(w.pstep), desc->weight_stream, desc->weight_stream_bytes, &e->ps, nullptr);
     if (rc) {
@@ -542,6 +619,11 @@ int dfb_engine_step(void* engine, void* stream) {
     return DFB_ERR_ARG;
   }
   return ((Engine*)engine)->step((cudaStream_t)stream);
+}
+
+size_t dfb_engine_tp_exchange_bytes(int batch, int hidden, int tp_size) {
+  if (batch < 1 || hidden < 1 || tp_size < 2) return 0;
+  return ((size_t)2 * tp_size * batch * hidden + (size_t)tp_size * batch * 2) * 8;
 }
 
 int dfb_engine_num_segments(void* engine) { return engine ? ((Engine*)engine)->num_segments() : 0; }

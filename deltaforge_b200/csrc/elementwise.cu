@@ -121,6 +121,79 @@ __global__ void add_partial_kernel(bf16* h, const float* sum, long n) {
   h[i] = f2bf(__fadd_rn(bf2f(h[i]), round_bf16(sum[i])));
 }
 
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Poll one exchange word until it carries `epoch`; gives up after about 0.14 s and records a code.
+__device__ __forceinline__ bool tp_wait_word(const unsigned long long* p, unsigned epoch, float& value, int* status) {
+  unsigned long long v = ld_sys_u64(p);
+  if ((unsigned)(v >> 32) != epoch) {
+    const long long t0 = clock64();
+    for (;;) {
+      v = ld_sys_u64(p);
+      if ((unsigned)(v >> 32) == epoch) break;
+      if (clock64() - t0 > (1LL << 28)) {
+        if (status) atomicCAS(status, 0, 50);
+        value = 0.f;
+        return false;
+      }
+      __nanosleep(40);
+    }
+  }
+  value = __uint_as_float((unsigned)v);
+  return true;
+}
+
+__global__ void tp_reduce_kernel(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
+                                 int epoch_off, int* status) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned epoch = *epoch_ctr * 256u + (unsigned)epoch_off;
+  float sum = 0.f;
+  bool ok = true;
+  for (int r = 0; r < tp_size; ++r) {  // rank order: every rank adds the same numbers in the same order
+    float v;
+    ok = tp_wait_word(slots + word_off + (long)r * n + i, epoch, v, status) && ok;
+    sum += v;
+  }
+  if (ok) h[i] = f2bf(__fadd_rn(bf2f(h[i]), round_bf16(sum)));
+}
+
+__global__ void tp_pick_kernel(const bf16* logits, int vocab_local, int batch, int tp_rank, TpPeer peer, const unsigned long long* my_slots,
+                               int64_t* tokens, int64_t* hist, const int* pos, int* status) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const unsigned epoch = *peer.epoch_ctr * 256u + (unsigned)peer.epoch_off;
+  const int local = (int)tokens[b];
+  const float best = bf2f(logits[(long)b * vocab_local + local]);
+  const unsigned gidx = (unsigned)(local + tp_rank * vocab_local);
+  const unsigned long long wv = ((unsigned long long)epoch << 32) | __float_as_uint(best);
+  const unsigned long long wi = ((unsigned long long)epoch << 32) | gidx;
+  const long at = peer.word_off + ((long)tp_rank * batch + b) * 2;
+  for (int k = 0; k < peer.tp_size; ++k) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peer.slots[k] + at), "l"(wv) : "memory");
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peer.slots[k] + at + 1), "l"(wi) : "memory");
+  }
+  float top = -INFINITY;
+  unsigned pick = 0xffffffffu;
+  bool ok = true;
+  for (int r = 0; r < peer.tp_size; ++r) {
+    float v, fi;
+    const unsigned long long* src = my_slots + peer.word_off + ((long)r * batch + b) * 2;
+    ok = tp_wait_word(src, epoch, v, status) && ok;
+    ok = tp_wait_word(src + 1, epoch, fi, status) && ok;
+    const unsigned idx = __float_as_uint(fi);
+    if (v > top || (v == top && idx < pick)) top = v, pick = idx;
+  }
+  if (!ok) return;
+  tokens[b] = pick;
+  if (hist) hist[(long)(*pos) * batch + b] = pick;
+}
+
+__global__ void bump_kernel(unsigned* counter) { *counter += 1u; }
+
 // Row gather of the embedding table (src/deltaforge/reference.py:804).
 __global__ void __launch_bounds__(128) embed_kernel(const bf16* table, const int64_t* tokens, int hidden, bf16* out, float* ss_out,
                                                     int ss_count) {
@@ -267,6 +340,25 @@ int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s) {
   if (n <= 0) return 0;
   add_partial_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(h, sum, n);
   return check_launch("add_partial");
+}
+
+int launch_tp_reduce(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
+                     int epoch_off, int* status, cudaStream_t s) {
+  if (n <= 0) return 0;
+  tp_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(h, slots, tp_size, n, word_off, epoch_ctr, epoch_off, status);
+  return check_launch("tp_reduce");
+}
+
+int launch_tp_pick(const bf16* logits, int vocab_local, int batch, int tp_rank, const TpPeer& peer, const unsigned long long* my_slots,
+                   int64_t* tokens, int64_t* hist, const int* pos, int* status, cudaStream_t s) {
+  if (batch <= 0) return 0;
+  tp_pick_kernel<<<(batch + 63) / 64, 64, 0, s>>>(logits, vocab_local, batch, tp_rank, peer, my_slots, tokens, hist, pos, status);
+  return check_launch("tp_pick");
+}
+
+int launch_bump(unsigned* counter, cudaStream_t s) {
+  bump_kernel<<<1, 1, 0, s>>>(counter);
+  return check_launch("bump");
 }
 
 int elementwise_configure() {

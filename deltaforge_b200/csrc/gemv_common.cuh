@@ -42,6 +42,15 @@ __device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
 
 // Output element (r, n) from its fp32 sum; returns the value stored (as fp32).
 __device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int n, float sum) {
+  if (p.epilogue == EPI_PARTIAL_PEER) {
+    // one 8-byte store per rank: the value and the epoch arrive together, the receiver needs no fence
+    const unsigned epoch = *p.peer.epoch_ctr * 256u + (unsigned)p.peer.epoch_off;
+    const unsigned long long w = ((unsigned long long)epoch << 32) | __float_as_uint(sum);
+    const long at = p.peer.word_off + (long)r * p.N + n;
+    for (int k = 0; k < p.peer.tp_size; ++k)
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.peer.slots[k] + at), "l"(w) : "memory");
+    return sum;
+  }
   if (p.epilogue == EPI_PARTIAL_F32) {
     ((float*)p.out)[(long)r * p.out_stride + n] = sum;
     return sum;

@@ -12,7 +12,21 @@ typedef __nv_bfloat16 bf16;
 
 enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 // EPI_PARTIAL_F32 (engine-internal, tensor parallelism): `out` is an fp32 buffer that receives the unrounded sum
-enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2, EPI_PARTIAL_F32 = 3 };
+// EPI_PARTIAL_PEER (engine-internal): the unrounded sum goes, tagged with an epoch, straight into a slot of every
+// rank's exchange buffer (peer stores over NVLink); see TpPeer
+enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2, EPI_PARTIAL_F32 = 3, EPI_PARTIAL_PEER = 4 };
+
+// Where the K-sharded projections of a tensor-parallel rank leave their partial sums when the ranks exchange
+// them by peer stores: slots[r] is rank r's exchange buffer (8-byte words {fp32 bits, epoch}); this rank
+// writes word word_off + row * N + n of every rank's buffer. The epoch is *epoch_ctr * 256 + epoch_off.
+constexpr int TP_MAX = 8;
+struct TpPeer {
+  unsigned long long* slots[TP_MAX];
+  int tp_size;
+  const unsigned* epoch_ctr;
+  int epoch_off;
+  long word_off;
+};
 // MATH_FAST sums x*q per scale group and applies the fp32 scale once per group (the weight is
 // never rounded to bf16); MATH_EXACT rounds every dequantised weight to bf16 before the product,
 // as the reference's expression does.
@@ -56,6 +70,7 @@ struct GemvParams {
   float* ss_out;
   const float* ss_in;
   int ss_count;
+  TpPeer peer;  // EPI_PARTIAL_PEER only
 };
 
 // Bytes of scratch the split-K path needs for a problem, and the number of counters.
@@ -215,6 +230,14 @@ int configure_kernels();
 int launch_advance(int* pos, int by, cudaStream_t s);
 // h <- bf16(h + bf16(sum)) over n elements: the residual add after an all-reduce of fp32 partial sums
 int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s);
+// The receiving side of the peer exchange: wait (bounded) for the tp words of every element to carry the epoch,
+// add them in rank order, round to bf16 and add to the residual stream. slots: this rank's own buffer.
+int launch_tp_reduce(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
+                     int epoch_off, int* status, cudaStream_t s);
+// Greedy pick across vocabulary shards by peer exchange of (best logit, global index); tokens holds the local index on entry.
+int launch_tp_pick(const bf16* logits, int vocab_local, int batch, int tp_rank, const TpPeer& peer, const unsigned long long* my_slots,
+                   int64_t* tokens, int64_t* hist, const int* pos, int* status, cudaStream_t s);
+int launch_bump(unsigned* counter, cudaStream_t s);
 
 }  // namespace dfb
 

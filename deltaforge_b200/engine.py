@@ -263,6 +263,8 @@ class DecodeEngine:
         math: int = MATH_FAST,
         persistent: bool = False,
         tp_size: int = 1,
+        tp_rank: int = 0,
+        tp_peer_slots: list[int] | None = None,
     ) -> None:
         """``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
         group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
@@ -331,7 +333,10 @@ class DecodeEngine:
         m.tokens, m.history, m.pos, m.logits = self.tokens.data_ptr(), self.history.data_ptr(), self.pos.data_ptr(), self.logits.data_ptr()
         m.attn_splits, m.math = self.attn_splits, math
         m.workspace, m.workspace_bytes = None, 0
-        m.tp_size = int(tp_size)
+        m.tp_size, m.tp_rank = int(tp_size), int(tp_rank)
+        if tp_peer_slots is not None:
+            self._peer_array = (C.c_void_p * len(tp_peer_slots))(*tp_peer_slots)
+            m.tp_peer_slots = C.cast(self._peer_array, C.POINTER(C.c_void_p))
         m.persistent = int(persistent)
         self.persistent = bool(persistent)
         if persistent:

@@ -161,20 +161,41 @@ class TensorParallelEngine:
     ``group`` is a ``torch.distributed`` process group whose backend can reduce CUDA tensors (NCCL).
     """
 
-    def __init__(self, local_weights: ModelWeights, cache: DecodeCache, *, rank: int, tp: int, group=None) -> None:
+    def __init__(self, local_weights: ModelWeights, cache: DecodeCache, *, rank: int, tp: int, group=None, exchange: str = "nccl") -> None:
+        """``exchange``: ``"nccl"`` adds the partial sums with ``torch.distributed.all_reduce`` between segments;
+        ``"peer"`` gives every rank a symmetric exchange buffer (``torch.distributed._symmetric_memory``) and lets
+        the kernels store into their peers' buffers and wait for one another: no collective call remains and the
+        whole token is one CUDA graph of this library's kernels. ``"peer"`` needs one GPU per rank."""
         import torch.distributed as dist
 
-        self.dist, self.group, self.rank, self.tp = dist, group, rank, tp
-        self.engine = DecodeEngine(local_weights, cache, tp_size=tp)
-        self.lib = self.engine.lib
+        if exchange not in ("nccl", "peer"):
+            raise ValueError(f"exchange must be 'nccl' or 'peer', got {exchange!r}")
+        self.dist, self.group, self.rank, self.tp, self.exchange = dist, group, rank, tp, exchange
         self.cache = cache
-        dev = self.engine.device
         self.vocab_local = local_weights.config.vocab_size
         hidden = local_weights.config.hidden_size
-        ptr = self.lib.dfb_engine_partial_buffer(self.engine._handle)
-        off = ptr - self.engine.workspace.data_ptr()
-        n = self.engine.batch * hidden
-        self.partial = self.engine.workspace[off : off + 4 * n].view(torch.float32)  # the fp32 partial sums, in place
+        peer_ptrs = None
+        if exchange == "peer":
+            import torch.distributed._symmetric_memory as symm_mem
+
+            lib = _lib.load()
+            dev = local_weights.embed.device
+            nbytes = lib.dfb_engine_tp_exchange_bytes(cache.batch_size, hidden, tp)
+            self.exchange_buffer = symm_mem.empty(nbytes // 8, dtype=torch.int64, device=dev)
+            self.exchange_buffer.zero_()
+            torch.cuda.synchronize(dev)
+            handle = symm_mem.rendezvous(self.exchange_buffer, group if group is not None else dist.group.WORLD)
+            peer_ptrs = [int(p) for p in handle.buffer_ptrs]
+            self._symm_handle = handle
+            dist.barrier(group=group)  # every rank's buffer is zeroed and mapped before anyone stores into it
+        self.engine = DecodeEngine(local_weights, cache, tp_size=tp, tp_rank=rank, tp_peer_slots=peer_ptrs)
+        self.lib = self.engine.lib
+        dev = self.engine.device
+        if exchange == "nccl":
+            ptr = self.lib.dfb_engine_partial_buffer(self.engine._handle)
+            off = ptr - self.engine.workspace.data_ptr()
+            n = self.engine.batch * hidden
+            self.partial = self.engine.workspace[off : off + 4 * n].view(torch.float32)  # the fp32 partial sums, in place
         self.segments = self.lib.dfb_engine_num_segments(self.engine._handle)
         self.best = torch.zeros((self.engine.batch, 2), dtype=torch.float32, device=dev)
         self.gathered = torch.zeros((tp, self.engine.batch, 2), dtype=torch.float32, device=dev)
@@ -204,6 +225,8 @@ class TensorParallelEngine:
         first call still runs directly (that also sets NCCL's channels up) and from the second call on one CUDA
         graph per token, collectives included, is replayed."""
         eng = self.engine
+        if self.exchange == "peer":  # the engine's own step: kernels only
+            return eng.step(tokens, graph=graph)
         self.cache.ensure_capacity(1)
         eng._sync_position()
         eng._set_tokens(tokens)
@@ -222,6 +245,8 @@ class TensorParallelEngine:
 
     def decode(self, tokens: Tensor, steps: int, *, graph: bool = False) -> Tensor:
         """Greedy loop on the device: returns the chosen tokens ``[batch, steps]`` (identical on every rank)."""
+        if self.exchange == "peer":
+            return self.engine.decode(tokens, steps)
         out = []
         t = tokens
         for _ in range(steps):

@@ -312,6 +312,16 @@ typedef struct dfb_model_desc {
    * adding into the residual stream, the caller adds that buffer across ranks (an all-reduce on the same
    * stream) between dfb_engine_step_segment() calls, and picks the token across the vocabulary shards itself. */
   int32_t tp_size;
+  int32_t tp_rank;
+  /* Optional, with tp_size > 1: host array of tp_size device pointers, entry r = rank r's exchange buffer of
+   * dfb_engine_tp_exchange_bytes() zeroed bytes, each mapped into this process (peer access over NVLink; entry
+   * tp_rank is this rank's own). With it the ranks exchange inside the kernels: the K-sharded projections
+   * store their fp32 partial sums, tagged with an epoch, straight into every rank's buffer, the next kernel
+   * waits (bounded, reporting through the status word) for all ranks' words, adds them in rank order and adds
+   * the result to the residual stream; the token is picked across shards the same way. No collective library
+   * call remains, dfb_engine_step / capture / replay / decode_host work as for one GPU, and every rank must
+   * run the same number of steps. One rank per GPU: kernels of different ranks wait on one another. */
+  void* const* tp_peer_slots;
 } dfb_model_desc;
 
 size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc);
@@ -330,6 +340,8 @@ int dfb_engine_step(void* engine, void* stream);
 int dfb_engine_num_segments(void* engine);
 int dfb_engine_step_segment(void* engine, int segment, void* stream);
 void* dfb_engine_partial_buffer(void* engine);
+/* Bytes of one rank's exchange buffer for tp_peer_slots. */
+size_t dfb_engine_tp_exchange_bytes(int batch, int hidden, int tp_size);
 /* Capture one step into a CUDA graph (the position is read from device memory, so one graph serves
  * every token; the reference re-records per step, src/deltaforge/kernels/static_cache.py:62-74). */
 int dfb_engine_capture(void* engine, void* stream);

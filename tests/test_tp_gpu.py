@@ -19,7 +19,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank: int, world: int, port: int, results, two_devices: bool):
+def _rank_main(rank: int, world: int, port: int, results, two_devices: bool, exchange: str = "nccl"):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dev = torch.device("cuda", rank if two_devices else 0)
     torch.cuda.set_device(dev)
@@ -57,12 +57,13 @@ def _rank_main(rank: int, world: int, port: int, results, two_devices: bool):
                 lt["conv"].copy_(wt["conv"][:, rows])
                 lt["recurrent"].copy_(wt["recurrent"][:, v0:v1])
         cache.seq_len = ctx_len
-        eng = TP.TensorParallelEngine(TP.shard_weights(full, rank, world), cache, rank=rank, tp=world)
+        eng = TP.TensorParallelEngine(TP.shard_weights(full, rank, world), cache, rank=rank, tp=world, exchange=exchange)
         tok = torch.tensor([17], device=dev)
         tp_logits, tp_tokens = [], []
         t = tok
-        for _ in range(steps):  # first step direct, the rest through the captured graph
-            local = eng.step(t).clone()  # segments and collectives launched directly
+        for i in range(steps):
+            # collectives: launched directly; peer exchange: the first step directly, the rest as one graph replay
+            local = eng.step(t, graph=(exchange == "peer" and i > 0)).clone()
             gathered = [torch.zeros_like(local) for _ in range(world)]
             dist.all_gather(gathered, local)
             tp_logits.append(torch.cat(gathered, dim=-1))
@@ -93,12 +94,12 @@ def _rank_main(rank: int, world: int, port: int, results, two_devices: bool):
         dist.destroy_process_group()
 
 
-def test_tensor_parallel_two_ranks_match_single_gpu():
+def _run_two_ranks(exchange: str):
     ctx = mp.get_context("spawn")
     results = ctx.Queue()
     port = 29700 + int(torch.randint(0, 200, (1,)).item())
     two = torch.cuda.device_count() >= 2
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, results, two)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, results, two, exchange)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -111,3 +112,13 @@ def test_tensor_parallel_two_ranks_match_single_gpu():
     assert all(p.exitcode == 0 for p in procs)
     ok, msg = results.get(timeout=10)
     assert ok, msg
+
+
+def test_tensor_parallel_two_ranks_match_single_gpu():
+    _run_two_ranks("nccl")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="kernels of different ranks wait on one another: one GPU per rank")
+def test_tensor_parallel_peer_exchange_matches_single_gpu():
+    """The ranks add their partial sums and pick the token by peer stores inside the kernels (no collective call)."""
+    _run_two_ranks("peer")
