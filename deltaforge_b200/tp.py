@@ -12,8 +12,13 @@ added across ranks in fp32 (two all-reduces per layer), and the sum is rounded t
 residual stream exactly where the unsharded projection would have been. Norm weights, the embedding table
 and the residual stream are replicated. Greedy sampling compares each rank's best logit.
 
-The collective is NCCL through ``torch.distributed`` on the engine's stream; kernels and collectives can be
-recorded into one CUDA graph per token (``graph=True``).
+Two forms of the exchange. ``exchange="nccl"``: the partial sums are added by ``torch.distributed.all_reduce``
+on the engine's stream between segments; kernels and collectives can be recorded into one CUDA graph per
+token (``graph=True``). ``exchange="peer"``: the K-sharded projection's epilogue stores every partial sum,
+tagged with an epoch, into a buffer of every rank (symmetric memory), and the next kernel polls its own
+buffer (bounded) and adds the ranks' values in rank order; the token pick exchanges (logit, index) the same
+way. No collective call remains and the token is one CUDA graph of this library's kernels. The peer form
+needs one GPU per rank, because the ranks' kernels wait on one another.
 """
 
 from __future__ import annotations
