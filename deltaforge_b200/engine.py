@@ -375,7 +375,10 @@ class DecodeEngine:
         code = C.c_int(0)
         _lib.check(self.lib.dfb_engine_status(self._handle, C.byref(code), self._stream()), "dfb_engine_status")
         if code.value:
-            raise _lib.Dfb200Error(f"a decode kernel reported status {code.value}: a bounded wait on an asynchronous copy ran out")
+            raise _lib.Dfb200Error(
+                f"a decode kernel reported status {code.value}: a bounded wait ran out "
+                "(50: a tensor-parallel peer's partial sums never arrived; other codes: an asynchronous copy)"
+            )
 
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream

@@ -122,3 +122,28 @@ def test_tensor_parallel_two_ranks_match_single_gpu():
 def test_tensor_parallel_peer_exchange_matches_single_gpu():
     """The ranks add their partial sums and pick the token by peer stores inside the kernels (no collective call)."""
     _run_two_ranks("peer")
+
+
+def test_peer_exchange_wait_runs_out_and_reports_status():
+    """A rank whose peer never shows up: the wait for the peer's partial sums is bounded (about 0.14 s per
+    kernel), the kernels return, the engine's status word says 50 and the CUDA context stays usable. The
+    'peer' here is a second local buffer that nothing fills, so no kernel waits for another kernel."""
+    from deltaforge_b200 import _lib
+    from deltaforge_b200 import engine as E
+    from deltaforge_b200 import synth
+    from deltaforge_b200 import tp as TP
+    from deltaforge_b200.config import ModelConfig, hybrid_layer_types
+
+    dev = torch.device("cuda", 0)
+    cfg = ModelConfig(hidden_size=2560, intermediate_size=9216, num_hidden_layers=4, vocab_size=4096, layer_types=hybrid_layer_types(4))
+    full = synth.random_model_weights(cfg, seed=3, device=dev, scale_dtype=torch.bfloat16)
+    cache = E.DecodeCache(TP.shard_config(cfg, 2), 1, 64, device=dev)
+    nbytes = _lib.load().dfb_engine_tp_exchange_bytes(1, cfg.hidden_size, 2)
+    mine = torch.zeros(nbytes // 8, dtype=torch.int64, device=dev)
+    absent = torch.zeros_like(mine)  # where rank 1's buffer would be mapped; rank 1's slots of `mine` stay empty
+    eng = E.DecodeEngine(TP.shard_weights(full, 0, 2), cache, tp_size=2, tp_rank=0, tp_peer_slots=[mine.data_ptr(), absent.data_ptr()])
+    eng.step(torch.tensor([17], device=dev), graph=False)
+    with pytest.raises(_lib.Dfb200Error, match="status 50"):
+        eng.check_status()
+    assert int(absent.ne(0).sum()) > 0  # rank 0 did store its partial sums into the peer's buffer
+    assert float(torch.ones(8, device=dev).sum()) == 8.0  # the context still works
