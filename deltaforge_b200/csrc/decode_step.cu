@@ -255,7 +255,10 @@ struct Engine {
       q.gate_swish = m.gate_is_swish;
       q.scale = 1.0f / sqrtf((float)d_);
       q.splits = m.attn_splits;
-      q.cluster_size = std::min(m.attn_splits, 4);  // these CTAs fill an SM each: small clusters schedule sooner
+      // these CTAs fill an SM each: small clusters schedule sooner; the last merge takes at most 16 clusters,
+      // so the longest caches of a one-KV-head shard (128 slices) use clusters of 8
+      q.cluster_size = std::min(m.attn_splits, 4);
+      while (q.cluster_size < 8 && m.attn_splits / q.cluster_size > 16) q.cluster_size *= 2;
       if (m.attn_splits > 1) {
         char* sc = at(ws.attn);
         q.part_acc = (float*)sc;

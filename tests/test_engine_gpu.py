@@ -156,6 +156,21 @@ def test_full_width_layers_match_oracle(math, persistent):
     assert eng.launches_per_step == (1 if persistent else 1 + 4 * 5 + 3)
 
 
+def test_one_kv_head_shard_with_a_long_cache_takes_128_slices():
+    """What a rank of four tensor-parallel ranks sees at 8K tokens of context: one KV head, and a cache long
+    enough that the fused attention step cuts it into 128 slices (16 clusters of 8)."""
+    import dataclasses
+
+    cfg = dataclasses.replace(qwen_width_config(), num_attention_heads=4, num_key_value_heads=1)
+    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=3, max_seq=8448, math=E.MATH_EXACT, persistent=False)
+    eng = cand.decode_engine(cc)
+    assert eng.attn_splits == 128
+    eng.check_status()
+    scale = ref.float().std().item()
+    assert (ref.float() - got.float()).abs().max().item() < 8e-2 * scale
+    assert_caches_close(oc, cc, atol_state=2e-2)
+
+
 def test_batch_of_eight_runs_the_tensor_core_projections_and_matches_oracle():
     """Eight sequences: every projection goes through the tcgen05 product (weights dequantised to exactly the
     reference's bf16 values), with the norm / SwiGLU / conv steps as separate kernels around it."""
