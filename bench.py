@@ -294,7 +294,7 @@ def run_ours(args) -> dict | None:
     cache = E.DecodeCache(cfg, BATCH, CONTEXT + steps + warmup + 8, device=dev)
     synth.fill_cache(cache, CONTEXT, seed=77 + rank)
     snap = cache.snapshot()
-    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent")
+    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent", prefetch_distance=args.prefetch_distance)
     tok = torch.full((BATCH,), 1000 + rank, dtype=torch.int64, device=dev)
     eng.capture()
 
@@ -343,6 +343,18 @@ def run_ours(args) -> dict | None:
     head_ms, head_bytes = time_head_gemv(weights) if rank == 0 else (0.0, 0)
     if rank != 0:
         return None
+    if args.timeline and args.engine == "graph":
+        # after every timed region: re-capture the step with the per-CTA timestamp marks on, run a few tokens, and
+        # write one row per launch of the last one
+        from deltaforge_b200 import timeline as TL
+
+        cache.restore(snap)
+        trace = eng.set_trace()
+        eng.decode(tok, 4)
+        torch.cuda.synchronize()
+        rows = TL.summarise(trace, TL.launch_names(list(cfg.layer_types), eng.launches_per_step))
+        Path(args.timeline).write_text(TL.render(rows) + "\n")
+        eng.set_trace(0)
     peak, peak_kind = measured_peaks()
     bytes_step = decode_bytes_per_step(cfg, batch=BATCH, context=CONTEXT, scale_bytes=2)
     ms_per_step = ms_max / steps
@@ -497,6 +509,9 @@ def main() -> None:
     ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
     ap.add_argument("--tp-exchange", choices=("nccl", "peer"), default="nccl", help="with --tp: how the ranks add their partial sums")
     ap.add_argument("--tp-graph", action="store_true", help="with --tp: record kernels and collectives into one CUDA graph per token")
+    ap.add_argument("--timeline", default=None, help="after the timed runs, write a per-launch timeline of one step to this file")
+    ap.add_argument("--prefetch-distance", type=int, default=None,
+                    help="projections ahead for which the step's kernels ask the L2 for weights (0: off; default: the library's)")
     ap.add_argument("--batch", type=int, default=None, help="sequences per GPU (default 1: the metric's configuration)")
     ap.add_argument("--context", type=int, default=None, help="tokens already in the cache (default 4096)")
     args = ap.parse_args()

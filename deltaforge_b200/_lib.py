@@ -6,6 +6,7 @@ There is no fallback: if the library cannot be loaded, or a call returns non-zer
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from . import build as _build
@@ -135,6 +136,8 @@ SIGNATURES = {
     "dfb_engine_decode_host": (C.c_int, [c_vp, c_vp, C.c_int, c_vp, c_vp]),
     "dfb_engine_status": (C.c_int, [c_vp, C.POINTER(C.c_int), c_vp]),
     "dfb_engine_launches_per_step": (C.c_int, [c_vp]),
+    "dfb_engine_set_prefetch_distance": (C.c_int, [c_vp, C.c_int]),
+    "dfb_engine_set_trace": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int]),
 }
 
 _lib: C.CDLL | None = None
@@ -160,6 +163,13 @@ def load() -> C.CDLL:
             raise RuntimeError(
                 f"libdfb200.so is not built and cannot be built here ({exc}). This package has no "
                 "CPU or PyTorch fallback; run `python -m deltaforge_b200.build` on a machine with nvcc."
+            ) from exc
+        # An older library is there but the sources changed and the rebuild failed: its struct layouts may no
+        # longer match the ctypes declarations above, so loading it is an explicit choice, never a default.
+        if not _build.is_current() and os.environ.get("DFB200_ALLOW_STALE_LIBRARY") != "1":
+            raise RuntimeError(
+                f"libdfb200.so is older than its sources and rebuilding it failed ({exc}); refusing to load it "
+                "(set DFB200_ALLOW_STALE_LIBRARY=1 to load the stale library anyway)"
             ) from exc
         path = _build.LIB
     lib = C.CDLL(str(path))

@@ -6,6 +6,7 @@
 
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -54,13 +55,23 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: libdfb200.so cannot be built on this machine")
-    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *map(str, sources()), "-o", str(LIB)]
-    proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
-    if verbose:
-        print(proc.stderr)
-    STAMP.write_text(_fingerprint())
+    # Several processes (the ranks of one torchrun job) may find a stale library at the same moment: one of them
+    # compiles, into a temporary file that replaces the library atomically, the others wait on the lock and then
+    # find the stamp current.
+    with open(PKG / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current():
+            return LIB
+        tmp = PKG / f".libdfb200.{os.getpid()}.so.tmp"
+        cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *map(str, sources()), "-o", str(tmp)]
+        proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+        if proc.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
+        if verbose:
+            print(proc.stderr)
+        os.replace(tmp, LIB)
+        STAMP.write_text(_fingerprint())
     return LIB
 
 

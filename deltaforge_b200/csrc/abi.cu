@@ -291,7 +291,8 @@ int dfb_attn_step(const dfb_attn_step_desc* d, void* stream) {
   p.out = (bf16*)d->out;
   p.out_stride = d->out_stride;
   p.status = d->status;
-  static const int configured = attn_step_configure();
+  static OncePerDevice once;
+  const int configured = once.run(attn_step_configure);
   if (configured) return configured;
   return launch_attn_step(p, (cudaStream_t)stream);
 }

@@ -346,7 +346,8 @@ int attn_configure() {
 
 int launch_attn_decode(const AttnParams& p, cudaStream_t stream) {
   if (p.batch <= 0) return 0;
-  static const int configured = attn_configure();
+  static OncePerDevice once;
+  const int configured = once.run(attn_configure);
   if (configured) return configured;
   if (p.hkv < 1 || p.hq % p.hkv) {
     set_error("attention decode: %d query heads do not divide into %d KV heads", p.hq, p.hkv);

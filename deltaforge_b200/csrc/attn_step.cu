@@ -153,6 +153,14 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   }
   __syncthreads();
   pdl_launch_dependents();
+  const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, nctas = gridDim.x * gridDim.y * gridDim.z;
+  if (t == 0) trace_mark(p.trace, cta, 0);
+  if (t == 32) {  // a slice of the weights a later GEMV of the step reads, into the L2
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (p.pf_ptr[i] != nullptr)
+        l2_prefetch_range(p.pf_ptr[i], p.pf_bytes[i] * (size_t)cta / nctas, p.pf_bytes[i] * (size_t)(cta + 1) / nctas);
+  }
   if (t == 0 && n_old > 0) {
     // old rows of the slice are contiguous in the cache: two bulk copies, in flight before the wait
     const uint64_t pol = make_evict_first_policy();
@@ -163,6 +171,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     bulk_copy(vst, p.vcache + off, bytes, bar, pol);
   }
   pdl_wait();
+  if (t == 0) trace_mark(p.trace, cta, 1);
 
   // queries of this KV head's group (warps 0..GROUPS-1), new key (warp GROUPS) and value (warp GROUPS+1)
   const int qw = p.attn_output_gate ? 2 * D : D;
@@ -195,6 +204,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   if (n_old > 0) ok = mbar_wait(bar, 0);
   if (!ok && t == 0 && p.status) atomicExch(p.status, 5);
   __syncthreads();
+  if (t == 0) trace_mark(p.trace, cta, 2);
 
   float qr[GROUPS][8];
 #pragma unroll
@@ -239,6 +249,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     }
   }
   __syncthreads();  // everyone is done with the staged slice; its memory becomes the warp-merge buffer
+  if (t == 0) trace_mark(p.trace, cta, 3);
 
   // merge the 8 warps: afterwards thread t owns head dim t of every query head
 #pragma unroll
@@ -279,6 +290,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
       }
     }
     cluster_barrier();
+    if (t == 0) trace_mark(p.trace, cta, 5);
     if (rank != 0) return;
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
@@ -361,6 +373,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     }
     p.out[(long)b * p.out_stride + (long)(hq0 + g) * D + t] = f2bf(y);
   }
+  if (t == 0) trace_mark(p.trace, cta, 6);
 }
 
 template <int GROUPS>

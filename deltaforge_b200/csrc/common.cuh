@@ -9,9 +9,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-namespace dfb {
+#include <mutex>
 
-typedef __nv_bfloat16 bf16;
+#include "kernels.h"
+
+namespace dfb {
 
 __device__ __forceinline__ float bf2f(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ bf16 f2bf(float v) { return __float2bfloat16_rn(v); }
@@ -64,10 +66,54 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void* p, uint64_t pol) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Ask the L2 to fetch [ptr + begin, ptr + end) from HBM without bringing it to the SM (bytes are rounded
+// inwards to 16-byte units, pieces of at most 16 KB). Used to start the weight stream of the NEXT kernel of
+// the decode step while this one is still working through its own dependent chain.
+__device__ __forceinline__ void l2_prefetch_range(const void* ptr, size_t begin, size_t end) {
+  const char* a = (const char*)ptr + ((begin + 15) & ~(size_t)15);
+  const char* e = (const char*)ptr + (end & ~(size_t)15);
+  while (a < e) {
+    const size_t left = (size_t)(e - a);
+    const uint32_t n = left > 16384 ? 16384u : (uint32_t)left;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"(n) : "memory");
+    a += n;
+  }
+}
+
+// Optional per-launch timeline for profiling the chain of dependent kernels: when `buf` is set, one thread of
+// each CTA stores the global nanosecond timer at up to TRACE_PHASES marks, at
+// buf[(slot * ctas + cta) * TRACE_PHASES + phase]. CTAs beyond `ctas` record nothing.
+__device__ __forceinline__ void trace_mark(const Trace& tr, int cta, int phase) {
+  if (tr.buf != nullptr && cta < tr.ctas) {
+    long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    tr.buf[((long)tr.slot * tr.ctas + cta) * TRACE_PHASES + phase] = ns;
+  }
+}
+
 // Error reporting shared by the C entry points (defined in abi.cu).
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 int check_int4_shape(int K, int N, int group);  // 0, or DFB_ERR_ARG with the message set
+
+// Kernel attributes (the opt-in to large dynamic shared memory, the carve-out preference) belong to the device
+// that is current when they are set, so set-up that a process would otherwise run once has to run once per
+// device: run(fn) calls fn the first time it is reached with a given device current and returns fn's code
+// (0 afterwards; a failed fn is tried again on the next call).
+struct OncePerDevice {
+  static constexpr int MAX_DEVICES = 64;
+  std::mutex mu;
+  bool done[MAX_DEVICES] = {};
+  int run(int (*fn)()) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return fn();
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev]) return 0;
+    const int rc = fn();
+    done[dev] = rc == 0;
+    return rc;
+  }
+};
 
 // Ask for the largest shared-memory carve-out for a kernel. Every kernel of the decode step does,
 // including those that use almost none: if consecutive kernels asked for different L1/shared splits

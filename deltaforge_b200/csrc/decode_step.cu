@@ -100,8 +100,46 @@ struct Engine {
   PStep* ps = nullptr;    // the persistent-kernel form of the step, when the model asked for it
   unsigned long long* peer_slots[TP_MAX] = {};  // tensor parallelism by peer stores: every rank's exchange buffer
   TpPeer cur_peer = {};                          // where the next EPI_PARTIAL_PEER projection writes
+  // The projections of one step in launch order, and which of them the next GEMV launch is: every kernel of
+  // the batch-1 step asks the L2 for the weights of the projection `pf_dist` GEMVs ahead (0: off).
+  std::vector<const dfb_linear*> order;
+  int cursor = 0;
+  int pf_dist = 1;
+  Trace trace = {};      // optional timeline buffer (dfb_engine_set_trace)
+  int trace_launches = 0;
 
   char* at(size_t off) const { return (char*)m.workspace + off; }
+
+  void plan_order() {
+    order.clear();
+    for (int i = 0; i < m.num_layers; ++i) {
+      order.push_back(&layers[i].in_proj);
+      order.push_back(&layers[i].out_proj);
+      order.push_back(&layers[i].gate_up);
+      order.push_back(&layers[i].down);
+    }
+    order.push_back(&m.head);
+  }
+  // Prefetch target for a launch that runs while GEMV number `idx` (of `order`) is the one to come `pf_dist`
+  // projections later. Only layer-sized weights: the LM head is 300 MB and streams at full rate by itself.
+  void aim_prefetch(const void** ptr, size_t* bytes, int idx) const {
+    ptr[0] = ptr[1] = nullptr;
+    bytes[0] = bytes[1] = 0;
+    if (pf_dist <= 0 || m.batch != 1 || m.tp_size > 1 || idx < 0 || idx >= (int)order.size()) return;
+    const dfb_linear& l = *order[idx];
+    const size_t wbytes = (size_t)l.K * l.N / 2;
+    if (!l.packed_k8 || wbytes > ((size_t)48 << 20)) return;
+    ptr[0] = l.packed_k8;
+    bytes[0] = wbytes;
+    ptr[1] = l.scale;
+    bytes[1] = (size_t)(l.K / l.group) * l.N * (l.scale_is_bf16 ? 2 : 4);
+  }
+  Trace launch_trace() const {
+    Trace t = trace;
+    t.slot = launches;
+    if (launches >= trace_launches) t.buf = nullptr;
+    return t;
+  }
 
   int gemv(const dfb_linear& l, const bf16* x, long x_stride, int prologue, const void* norm_w, const bf16* up,
            long up_stride, int epilogue, bf16* out, long out_stride, const dfb_layer_desc* conv_layer, cudaStream_t s) {
@@ -183,6 +221,9 @@ struct Engine {
     p.math = m.math;
     p.status = (int*)at(ws.status);
     if (epilogue == EPI_PARTIAL_PEER) p.peer = cur_peer;
+    aim_prefetch(p.pf_ptr, p.pf_bytes, cursor + pf_dist);
+    ++cursor;
+    p.trace = launch_trace();
     // Sum-of-squares hand-off along the residual stream (batch 1, cluster kernel on both sides).
     const int h_tiles = (m.hidden + cluster_tile_width(m.hidden) - 1) / cluster_tile_width(m.hidden);
     if (prologue == PRO_RMSNORM && x_is_h && ss_valid) {
@@ -221,6 +262,8 @@ struct Engine {
     d.state = L.recurrent;
     d.out = mix;
     d.out_stride = vd;
+    aim_prefetch(d.pf_ptr, d.pf_bytes, cursor + pf_dist - 1);
+    d.trace = launch_trace();
     ++launches;
     return launch_deltanet_step(d, s);
   }
@@ -270,6 +313,8 @@ struct Engine {
       q.out = mix;
       q.out_stride = (long)m.hq * d_;
       q.status = (int*)at(ws.status);
+      aim_prefetch(q.pf_ptr, q.pf_bytes, cursor + pf_dist - 1);
+      q.trace = launch_trace();
       ++launches;
       return launch_attn_step(q, s);
     }
@@ -449,7 +494,7 @@ struct Engine {
       set_error("engine: segment %d of %d (tensor-parallel engines only)", seg, num_segments());
       return DFB_ERR_ARG;
     }
-    if (seg == 0) launches = 0;
+    if (seg == 0) launches = cursor = 0;
     if (seg == 0) {
       if (int rc = embed(s)) return rc;
     } else {
@@ -475,6 +520,7 @@ struct Engine {
       return DFB_ERR_ARG;
     }
     launches = 0;
+    cursor = 0;
     if (int rc = embed(s)) return rc;
     for (int i = 0; i < m.num_layers; ++i) {
       if (int rc = first_half(i, s)) return rc;
@@ -572,6 +618,7 @@ int dfb_engine_create(const dfb_model_desc* desc, void** engine_out) {
   e->layers.assign(desc->layers_host, desc->layers_host + desc->num_layers);
   e->m.layers_host = e->layers.data();
   e->ws = w;
+  e->plan_order();
   if (desc->tp_size > 1) {
     if (desc->tp_size > TP_MAX || desc->tp_rank < 0 || desc->tp_rank >= desc->tp_size) {
       set_error("engine: tensor-parallel rank %d of %d (at most %d ranks)", desc->tp_rank, desc->tp_size, TP_MAX);
@@ -755,6 +802,28 @@ int dfb_engine_read_trace(void* engine, int64_t* out_host, int max_values, void*
     return -1;
   }
   return pstep_read_trace(e->ps, (long long*)out_host, max_values, (cudaStream_t)stream);
+}
+
+int dfb_engine_set_prefetch_distance(void* engine, int distance) {
+  Engine* e = (Engine*)engine;
+  if (!e || distance < 0 || distance > 8) {
+    set_error("dfb_engine_set_prefetch_distance: null engine or distance outside 0..8");
+    return DFB_ERR_ARG;
+  }
+  e->pf_dist = distance;
+  return DFB_OK;
+}
+
+int dfb_engine_set_trace(void* engine, int64_t* buffer, int max_launches, int ctas_per_launch) {
+  Engine* e = (Engine*)engine;
+  if (!e || max_launches < 0 || ctas_per_launch < 0 || (buffer && (max_launches == 0 || ctas_per_launch == 0))) {
+    set_error("dfb_engine_set_trace: null engine or bad sizes");
+    return DFB_ERR_ARG;
+  }
+  e->trace.buf = (long long*)buffer;
+  e->trace.ctas = ctas_per_launch;
+  e->trace_launches = buffer ? max_launches : 0;
+  return DFB_OK;
 }
 
 int dfb_engine_launches_per_step(void* engine) { return engine ? ((Engine*)engine)->launches : 0; }

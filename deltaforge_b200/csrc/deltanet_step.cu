@@ -91,6 +91,8 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   // still running: let the next kernel start its own prefetch, and touch nothing the GEMV writes
   // until griddepcontrol.wait below. The recurrent state is only ever written by this kernel.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int cta = blockIdx.y * gridDim.x + blockIdx.x, nctas = gridDim.x * gridDim.y;
+  if (t == 0) trace_mark(p.trace, cta, 0);
   // 1. The state slab goes in flight first; nothing below depends on it until delta_core.
   float* S = p.state + ((long)(b * p.num_v_heads + hv) * dk) * dv;
   float s[RPT];
@@ -99,8 +101,15 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     const int k = warp * RPT + i;
     s[i] = (col_ok && k < dk) ? __ldcs(S + (long)k * dv + col) : 0.f;
   }
+  if (t == 32) {  // a slice of the weights a later GEMV of the step reads, into the L2
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (p.pf_ptr[i] != nullptr)
+        l2_prefetch_range(p.pf_ptr[i], p.pf_bytes[i] * (size_t)cta / nctas, p.pf_bytes[i] * (size_t)(cta + 1) / nctas);
+  }
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (t == 0) trace_mark(p.trace, cta, 1);
   // 2. q, k of the key head: fp32, L2-normalised, query scaled by 1/sqrt(dk).
   const long row = (long)b * p.row_stride;
   {
@@ -156,6 +165,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     y = __fmul_rn(y, silu_f(zval));
     p.out[(long)b * p.out_stride + (long)hv * dv + col] = f2bf(y);
   }
+  if (t == 0) trace_mark(p.trace, cta, 6);
 }
 
 // Many sequences: one CTA owns a whole value head (all dv <= 128 columns, 64 state values per thread), so the

@@ -36,12 +36,47 @@ __device__ __forceinline__ float prologue_value(const GemvParams& p, int r, int 
   return xv;
 }
 
+// The same arithmetic on values already loaded: xv the activation, wv the norm weight (PRO_RMSNORM) or `up`
+// (PRO_SILU_MUL), both as the fp32 of their bf16.
+__device__ __forceinline__ float prologue_apply(int prologue, float xv, float wv, float rstd) {
+  if (prologue == PRO_RMSNORM) {
+    float v = __fmul_rn(xv, rstd);
+    v = __fmul_rn(v, __fadd_rn(1.0f, wv));
+    return round_bf16(v);
+  }
+  if (prologue == PRO_SILU_MUL) {
+    float s = round_bf16(silu_f(xv));
+    return round_bf16(__fmul_rn(s, wv));
+  }
+  return xv;
+}
+
 __device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
   return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
 }
 
+// What the epilogue of output element (r, n) reads besides the sum: loaded early, so that the loads are in
+// flight while the dot products run, and handed to epilogue_store_pre().
+struct EpiPre {
+  float res;             // EPI_RESIDUAL: the residual stream's value
+  float h0, h1, h2;      // EPI_CONV: the three older taps of the channel's history
+  float w0, w1, w2, w3;  // EPI_CONV: the channel's conv weights
+};
+__device__ __forceinline__ EpiPre epilogue_preload(const GemvParams& p, int r, int n) {
+  EpiPre e = {};
+  if (p.epilogue == EPI_RESIDUAL) {
+    e.res = bf2f(p.residual[(long)r * p.res_stride + n]);
+  } else if (p.epilogue == EPI_CONV && n < p.conv_dim) {
+    const bf16* st = p.conv_state + ((long)r * p.conv_dim + n) * 3;
+    const bf16* w = p.conv_w + (long)n * 4;
+    e.h0 = bf2f(st[0]), e.h1 = bf2f(st[1]), e.h2 = bf2f(st[2]);
+    e.w0 = bf2f(w[0]), e.w1 = bf2f(w[1]), e.w2 = bf2f(w[2]), e.w3 = bf2f(w[3]);
+  }
+  return e;
+}
+
 // Output element (r, n) from its fp32 sum; returns the value stored (as fp32).
-__device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int n, float sum) {
+__device__ __forceinline__ float epilogue_store_pre(const GemvParams& p, int r, int n, float sum, const EpiPre& pre) {
   if (p.epilogue == EPI_PARTIAL_PEER) {
     // one 8-byte store per rank: the value and the epoch arrive together, the receiver needs no fence
     const unsigned epoch = *p.peer.epoch_ctr * 256u + (unsigned)p.peer.epoch_off;
@@ -57,8 +92,7 @@ __device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int 
   }
   bf16 y = f2bf(sum);
   if (p.epilogue == EPI_RESIDUAL) {
-    float h = bf2f(p.residual[(long)r * p.res_stride + n]);
-    const bf16 o = f2bf(__fadd_rn(h, bf2f(y)));
+    const bf16 o = f2bf(__fadd_rn(pre.res, bf2f(y)));
     p.out[(long)r * p.out_stride + n] = o;
     return bf2f(o);
   }
@@ -66,22 +100,24 @@ __device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int 
     // 4-tap depthwise causal conv decode step (src/deltaforge/kernels/inline_causal_conv.py:111-129):
     // fp32 products summed left to right, rounded to bf16, then SiLU; history [h0,h1,h2] <- [h1,h2,x].
     bf16* st = p.conv_state + ((long)r * p.conv_dim + n) * 3;
-    const bf16* w = p.conv_w + (long)n * 4;
-    float h0 = bf2f(st[0]), h1 = bf2f(st[1]), h2 = bf2f(st[2]), xv = bf2f(y);
-    float acc = __fmul_rn(h0, bf2f(w[0]));
-    acc = __fadd_rn(acc, __fmul_rn(h1, bf2f(w[1])));
-    acc = __fadd_rn(acc, __fmul_rn(h2, bf2f(w[2])));
-    acc = __fadd_rn(acc, __fmul_rn(xv, bf2f(w[3])));
+    const float xv = bf2f(y);
+    float acc = __fmul_rn(pre.h0, pre.w0);
+    acc = __fadd_rn(acc, __fmul_rn(pre.h1, pre.w1));
+    acc = __fadd_rn(acc, __fmul_rn(pre.h2, pre.w2));
+    acc = __fadd_rn(acc, __fmul_rn(xv, pre.w3));
     float a = round_bf16(acc);
     const bf16 o = f2bf(silu_f(a));
     p.out[(long)r * p.out_stride + n] = o;
-    st[0] = st[1];
-    st[1] = st[2];
+    st[0] = f2bf(pre.h1);
+    st[1] = f2bf(pre.h2);
     st[2] = y;
     return bf2f(o);
   }
   p.out[(long)r * p.out_stride + n] = y;
   return bf2f(y);
+}
+__device__ __forceinline__ float epilogue_store(const GemvParams& p, int r, int n, float sum) {
+  return epilogue_store_pre(p, r, n, sum, epilogue_preload(p, r, n));
 }
 
 }  // namespace dfb

@@ -412,7 +412,8 @@ size_t gemv_counter_count(int rows, int K, int N, int group) {
 
 int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   if (p.rows <= 0 || p.N <= 0) return 0;
-  static const int configured = gemv_configure();
+  static OncePerDevice once;
+  const int configured = once.run(gemv_configure);
   if (configured) return configured;
   // eight rows and more: the weight tile is shared by enough rows for the tensor cores
   if (!p.force_tiled && p.rows >= 8 && tc_path_ok(p)) return launch_gemm_tc(p, p.status, stream);
@@ -481,7 +482,7 @@ static int static_scratch_for_current_device(void** out) {
     if (e != cudaSuccess || ptr == nullptr) {
       set_error("static-scratch gemv: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
       (void)cudaGetLastError();
-      return 3;
+      return 1;  // DFB_ERR_CUDA
     }
     g_static_ptr[dev] = ptr;
   }
@@ -533,7 +534,8 @@ extern "C" int dfb_int4_gemv_static(const dfb_gemv_desc* d, void* stream) {
               d->rows, d->K, d->N, partial_bytes, counters, (size_t)STATIC_PARTIALS_BYTES, (size_t)STATIC_COUNTERS);
     return 2;
   }
-  static const int configured = gemv_configure();
+  static OncePerDevice once;
+  const int configured = once.run(gemv_configure);
   if (configured) return configured;
   void* base = nullptr;
   if (int rc = static_scratch_for_current_device(&base)) return rc;

@@ -98,9 +98,9 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
 // Epilogue for column `tile * TNW + t` by the TNW threads that hold the tile's final sums; optionally
 // leaves the tile's sum of squares (of the values stored) for the next kernel's RMSNorm.
 template <int TNW>
-__device__ __forceinline__ void finish_tile(const GemvParams& p, int tile, int t, float v, float* wred) {
+__device__ __forceinline__ void finish_tile(const GemvParams& p, int tile, int t, float v, float* wred, const EpiPre& pre) {
   const int n = tile * TNW + t;
-  const float stored = n < p.N ? epilogue_store(p, 0, n, v) : 0.f;
+  const float stored = n < p.N ? epilogue_store_pre(p, 0, n, v, pre) : 0.f;
   if (p.ss_out == nullptr) return;
   const float sq = warp_sum(stored * stored);
   if ((t & 31) == 0) wred[t >> 5] = sq;
@@ -147,8 +147,10 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
   const int g0 = (int)((long)rank * G / cs), g1 = (int)((long)(rank + 1) * G / cs);
   const int nunits = g1 - g0;
   const uint32_t scale_bytes = p.scale_bf16 ? TNW * 2 : TNW * 4;
+  const int cta = blockIdx.x;
 
   if (t == 0) {
+    trace_mark(p.trace, cta, 0);
     for (int s = 0; s < nunits; ++s) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -156,6 +158,7 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   bool ok = true;
+  EpiPre pre = {};
   if (warp == CTHREADS / 32) {
     // producer: everything this CTA will read from the weight, at once (weights never depend on earlier kernels)
     if (lane == 0) {
@@ -166,9 +169,26 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
         tma_load_2d(dst, &wmap, tile * TNW, (g0 + s) * UROWS, &full[s], pol);
         tma_load_2d(dst + W_BYTES, &smap, tile * TNW, g0 + s, &full[s], pol);
       }
+      // with this CTA's own loads queued, start the L2 on a slice of what the next GEMV of the step will read
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (p.pf_ptr[i] != nullptr)
+          l2_prefetch_range(p.pf_ptr[i], p.pf_bytes[i] * (size_t)cta / gridDim.x, p.pf_bytes[i] * (size_t)(cta + 1) / gridDim.x);
+      trace_mark(p.trace, cta, 7);
     }
   } else {
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
+    if (t == 0) trace_mark(p.trace, cta, 1);
+    // Everything this CTA reads that an earlier kernel wrote goes in flight at once: the activation values of
+    // the first group each warp quantises, and what the epilogue adds to (rank 0 finishes the tile).
+    uint2 xraw = make_uint2(0u, 0u), wraw = make_uint2(0u, 0u);
+    if (warp < nunits) {
+      const int k = (g0 + warp) * 128 + lane * 4;
+      xraw = *(const uint2*)(p.x + k);
+      if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
+      if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
+    }
+    if ((cs == 1 || rank == 0) && t < TNW && tile * TNW + t < p.N) pre = epilogue_preload(p, 0, tile * TNW + t);
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
       float tot = 0.f;
@@ -193,9 +213,19 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
       const int g = g0 + gl;
       float v[4];
       float amax = 0.f;
+      if (gl != warp) {  // later groups of this warp (the first one's values are already here)
+        const int k = g * 128 + lane * 4;
+        xraw = *(const uint2*)(p.x + k);
+        if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
+        if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
+      }
+      const float xr[4] = {__uint_as_float(xraw.x << 16), __uint_as_float(xraw.x & 0xffff0000u), __uint_as_float(xraw.y << 16),
+                           __uint_as_float(xraw.y & 0xffff0000u)};
+      const float wr[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u), __uint_as_float(wraw.y << 16),
+                           __uint_as_float(wraw.y & 0xffff0000u)};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        v[i] = prologue_value(p, 0, g * 128 + lane * 4 + i, rstd);
+        v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
         amax = fmaxf(amax, fabsf(v[i]));
       }
       amax = warp_max(amax);
@@ -217,6 +247,7 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
       if ((lane & 1) == 0) mk[gl * UROWS + (lane >> 1)] = msum;
     }
     consumer_sync();
+    if (t == 0) trace_mark(p.trace, cta, 2);
 
     const int rl = t / CQ, cq = t % CQ;
     float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -259,27 +290,34 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
       }
     }
     if (!ok && lane == 0) atomicExch(a.status, 4);
+    if (t == 0) trace_mark(p.trace, cta, 3);
     // add the row lanes, then hand this CTA's column sums to rank 0
     *(float4*)(red + rl * TNW + cq * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
     consumer_sync();
+    if (t == 0) trace_mark(p.trace, cta, 4);
     if (t < TNW) {
       float v = 0.f;
 #pragma unroll
       for (int r = 0; r < RL; ++r) v += red[r * TNW + t];
       if (cs == 1) {
-        finish_tile<TNW>(p, tile, t, v, wred);
+        finish_tile<TNW>(p, tile, t, v, wred, pre);
       } else {
         dsmem_store(dsm + rank * TNW + t, 0, v);
       }
     }
   }
-  if (cs == 1) return;
+  if (cs == 1) {
+    if (t == 0) trace_mark(p.trace, cta, 6);
+    return;
+  }
   cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
+  if (t == 0) trace_mark(p.trace, cta, 5);
   if (rank == 0 && t < TNW) {
     float v = 0.f;
     for (int r = 0; r < cs; ++r) v += dsm[r * TNW + t];
-    finish_tile<TNW>(p, tile, t, v, wred);
+    finish_tile<TNW>(p, tile, t, v, wred, pre);
   }
+  if (t == 0) trace_mark(p.trace, cta, 6);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -386,7 +424,9 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
 // for 16-byte rows, and a per-CTA footprint that leaves room for several CTAs per SM.
 bool cluster_path_ok(const GemvParams& p) {
   if (!(p.rows == 1 && p.packed_k8 != nullptr && p.group == 128 && p.K % 256 == 0 && p.N % 4 == 0 &&
-        ((uintptr_t)p.packed_k8 % 16) == 0 && ((uintptr_t)p.scale % 16) == 0 && p.math == MATH_FAST))
+        ((uintptr_t)p.packed_k8 % 16) == 0 && ((uintptr_t)p.scale % 16) == 0 && p.math == MATH_FAST &&
+        ((uintptr_t)p.x % 8) == 0 && (p.prologue != PRO_RMSNORM || ((uintptr_t)p.norm_w % 8) == 0) &&
+        (p.prologue != PRO_SILU_MUL || ((uintptr_t)p.up % 8) == 0)))
     return false;
   const int cs = pick_cs(p.K), G = p.K / 128;
   const int max_units = (G + cs - 1) / cs;

@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
   const int u0 = (int)((long)c * a.units / P), u1 = (int)((long)(c + 1) * a.units / P);
 
   if (t == 0) {
+    trace_mark(p.trace, c, 0);
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CTHREADS / 32);
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
 
   // ---------------- consumers ----------------
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
+  if (t == 0) trace_mark(p.trace, c, 1);
 
   {
     float rstd = 1.f;
@@ -221,6 +223,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
     consumer_sync();
   }
 
+  if (t == 0) trace_mark(p.trace, c, 2);
   const int n0 = (t << 2);  // first of this thread's 4 columns inside the tile
   const int box_off = (t >> 6) * (RBK * BOXW * 4) + (t & 63) * 16;
   float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -330,6 +333,7 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const __grid_const
     sc_group = -1;
   }
   if (!ok && lane == 0) atomicExch(a.status, 3);
+  if (t == 0) trace_mark(p.trace, c, 6);
 }
 
 // reference layout [K/2, N] bytes (row j low nibble, row j + K/2 high nibble) -> [K/8, N] words

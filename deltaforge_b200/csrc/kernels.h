@@ -10,6 +10,14 @@ namespace dfb {
 
 typedef __nv_bfloat16 bf16;
 
+// Optional timeline of one launch (profiling): see trace_mark() in common.cuh. buf == nullptr: off.
+constexpr int TRACE_PHASES = 8;
+struct Trace {
+  long long* buf;
+  int slot;  // index of the launch within the step
+  int ctas;  // CTAs recorded per launch
+};
+
 enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 // EPI_PARTIAL_F32 (engine-internal, tensor parallelism): `out` is an fp32 buffer that receives the unrounded sum
 // EPI_PARTIAL_PEER (engine-internal): the unrounded sum goes, tagged with an epoch, straight into a slot of every
@@ -71,6 +79,11 @@ struct GemvParams {
   const float* ss_in;
   int ss_count;
   TpPeer peer;  // EPI_PARTIAL_PEER only
+  // Optional: up to two byte ranges (the words and the scales of the GEMV that follows in the step) that the
+  // CTAs of this launch ask the L2 to fetch, a slice each, once their own loads are issued.
+  const void* pf_ptr[2];
+  size_t pf_bytes[2];
+  Trace trace;
 };
 
 // Bytes of scratch the split-K path needs for a problem, and the number of counters.
@@ -118,6 +131,9 @@ struct DeltaNetParams {
   float* state;  // [batch, Hv, dk, dv] fp32, updated in place
   bf16* out;     // [batch, Hv*dv]
   long out_stride;
+  const void* pf_ptr[2];  // as in GemvParams
+  size_t pf_bytes[2];
+  Trace trace;
 };
 int launch_deltanet_step(const DeltaNetParams& p, cudaStream_t stream);
 
@@ -200,6 +216,9 @@ struct AttnStepParams {  // prep + split-KV decode + merge + gate in one launch 
   bf16* out;  // [batch, hq*d]
   long out_stride;
   int* status;  // device word set if the bounded wait on the staging copies gives up
+  const void* pf_ptr[2];  // as in GemvParams
+  size_t pf_bytes[2];
+  Trace trace;
 };
 bool attn_step_ok(int d, int hq, int hkv, int rotary_dim, int splits, int max_seq);
 int attn_step_configure();

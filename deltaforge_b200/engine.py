@@ -265,8 +265,11 @@ class DecodeEngine:
         tp_size: int = 1,
         tp_rank: int = 0,
         tp_peer_slots: list[int] | None = None,
+        prefetch_distance: int | None = None,
     ) -> None:
-        """``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
+        """``prefetch_distance``: how many projections ahead the kernels of a batch-1 step ask the L2 cache for
+        weights (``dfb_engine_set_prefetch_distance``; ``None`` keeps the library's default, 0 switches it off).
+        ``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
         group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
         cfg = weights.config
         self.config, self.weights, self.cache = cfg, weights, cache
@@ -352,6 +355,22 @@ class DecodeEngine:
         handle = C.c_void_p()
         _lib.check(self.lib.dfb_engine_create(C.byref(m), C.byref(handle)), "dfb_engine_create")
         self._handle = handle
+        if prefetch_distance is not None:
+            _lib.check(self.lib.dfb_engine_set_prefetch_distance(handle, int(prefetch_distance)), "dfb_engine_set_prefetch_distance")
+
+    def set_trace(self, max_ctas: int = 320) -> Tensor | None:
+        """Profiling: record per-CTA device timestamps of every launch of the steps captured or enqueued from now
+        on. Returns the int64 tensor ``(launches, max_ctas, 8)`` the kernels write (see ``dfb_engine_set_trace``
+        for the marks); ``max_ctas=0`` switches tracing off. Call before ``capture()``."""
+        if max_ctas <= 0:
+            _lib.check(self.lib.dfb_engine_set_trace(self._handle, None, 0, 0), "dfb_engine_set_trace")
+            self._trace = None
+            return None
+        launches = 16 + 8 * len(self.weights.layers)
+        self._trace = torch.zeros((launches, max_ctas, 8), dtype=torch.int64, device=self.device)
+        _lib.check(self.lib.dfb_engine_set_trace(self._handle, self._trace.data_ptr(), launches, max_ctas), "dfb_engine_set_trace")
+        self._captured = False
+        return self._trace
 
     # -- lifecycle -------------------------------------------------------------------------
 

@@ -363,6 +363,19 @@ int dfb_engine_status(void* engine, int* status_host, void* stream);
  * 16 last layer done, 17 LM head done. */
 int dfb_engine_trace_layer(void* engine, int layer);
 int dfb_engine_read_trace(void* engine, int64_t* out_host, int max_values, void* stream);
+/* How far ahead the kernels of a batch-1 step ask the L2 cache for weights: every launch requests, a slice
+ * per CTA, the int4 words and scales of the projection `distance` GEMVs after the one it runs (or precedes),
+ * so HBM keeps streaming while the kernels work through their dependent latencies. 0 switches it off; the
+ * default is 1. Takes effect for steps enqueued or captured afterwards. No counterpart in the reference
+ * (its kernels rely on the hardware's own prefetching, src/deltaforge/kernels/tiled_gemv.py:452-454). */
+int dfb_engine_set_prefetch_distance(void* engine, int distance);
+/* Profiling of the graph-of-kernels step: with `buffer` (device memory, max_launches * ctas_per_launch * 8
+ * int64, zeroed by the caller) set, one thread of every CTA of launch number l of a step stores %globaltimer
+ * (ns) at buffer[(l * ctas_per_launch + cta) * 8 + mark]; marks: 0 kernel entry, 1 the wait for the previous
+ * kernel returned, 2 activation ready in shared memory, 3 dot products done (all weights arrived), 4 CTA-level
+ * sums done, 5 cluster barrier passed, 6 exit, 7 this CTA's copies (and prefetches) issued. NULL switches it
+ * off. Applies to steps enqueued or captured afterwards. */
+int dfb_engine_set_trace(void* engine, int64_t* buffer, int max_launches, int ctas_per_launch);
 /* Number of kernel launches in one step. */
 int dfb_engine_launches_per_step(void* engine);
 

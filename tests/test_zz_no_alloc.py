@@ -92,6 +92,34 @@ def test_static_scratch_gemv_matches_caller_scratch_gemv(rows, k, n, math, fused
     assert not torch.isnan(first.float()).any()
     assert torch.equal(first, want)
     assert torch.equal(second, want)
+    # and against the CPU oracle's expression for the same problem (rtol 2e-2 of the value, atol 2e-2 of the mean magnitude)
+    from oracle import ref_ops as R
+
+    x = p["x"].cpu()
+    xin = R.rms_norm(x, p["norm_w"].cpu(), 1e-6) if fused else x
+    ref = R.dequant_gemv_int4(xin, p["packed"].cpu(), p["scale"].cpu(), p["group"])
+    if fused:
+        ref = p["residual"].cpu() + ref
+    err = (first.float().cpu() - ref.float()).abs()
+    assert bool((err <= 2e-2 * ref.float().abs() + 2e-2 * ref.float().abs().mean()).all())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second CUDA device in this process")
+def test_static_scratch_gemv_on_a_second_device_of_the_process():
+    """Kernel attributes are per device: the first call on device 1 must set them there too (four rows per CTA
+    take more dynamic shared memory than a kernel gets without the opt-in)."""
+    lib = _lib.load()
+    rows, k, n = 8, 2560, 1024
+    p0 = _problem(rows, k, n, 77)
+    want = _run_static(lib, p0, rows, k, n, MATH_FAST, False).cpu()
+    dev1 = torch.device("cuda", 1)
+    p1 = {key: (v.to(dev1) if torch.is_tensor(v) else v) for key, v in p0.items()}
+    with torch.cuda.device(dev1):
+        out = torch.full((rows, n), float("nan"), device=dev1, dtype=BF16)
+        d = _desc(p1, rows, k, n, out, MATH_FAST, False)
+        _lib.check(lib.dfb_int4_gemv_static(C.byref(d), None), "dfb_int4_gemv_static")
+        torch.cuda.synchronize(dev1)
+    assert torch.equal(out.cpu(), want)
 
 
 def test_static_scratch_gemv_alternating_sizes():
