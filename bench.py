@@ -341,9 +341,19 @@ def run_ours(args) -> dict | None:
     ms_max, e2e_ms_max = times.tolist()
 
     head_ms, head_bytes = time_head_gemv(weights) if rank == 0 else (0.0, 0)
+    launches_per_step, attn_splits = eng.launches_per_step, eng.attn_splits
+    tp_line = None
+    if dist is not None and not args.no_tp_arm and BATCH == 1:
+        # the multi-GPU run also reports the tensor-parallel form of the same model on the same GPUs
+        del eng, cache, snap
+        torch.cuda.empty_cache()
+        try:
+            tp_line = tp_arm(dist, rank, world, dev, min(steps, 64), min(warmup, 8), args.layers)
+        except Exception as exc:  # the data-parallel line stands on its own
+            tp_line = {"n": world, "error": f"{type(exc).__name__}: {exc}"[:400]}
     if rank != 0:
         return None
-    if args.timeline and args.engine == "graph":
+    if args.timeline and args.engine == "graph" and tp_line is None:
         # after every timed region: re-capture the step with the per-CTA timestamp marks on, run a few tokens, and
         # write one row per launch of the last one
         from deltaforge_b200 import timeline as TL
@@ -382,7 +392,7 @@ def run_ours(args) -> dict | None:
             "parallelism": f"independent sequences x{world}, no collectives",
             "l2": "each step streams 2.4 GB of weights, KV and state, 19x the 126 MB L2; no flush needed",
             "engine": args.engine,
-            "attn_splits": eng.attn_splits,
+            "attn_splits": attn_splits,
             "scale_dtype": "bf16",
         },
         "e2e": {
@@ -392,8 +402,8 @@ def run_ours(args) -> dict | None:
             "d2h_bytes_per_step": 8 * BATCH,
             "tokens_match_device_loop": same,
         },
-        "gpu_launches": steps * eng.launches_per_step,
-        "launches_per_step": eng.launches_per_step,
+        "gpu_launches": steps * launches_per_step,
+        "launches_per_step": launches_per_step,
         "clocks": clocks.summary(),
         "roofline": {
             "kernel": "gemv_stream_kernel (int4 GEMV, RMSNorm prologue) on the LM head 248320x2560",
@@ -421,7 +431,87 @@ def run_ours(args) -> dict | None:
         },
         "finite_logits": finite,
     }
+    if tp_line is not None:
+        line["tp"] = tp_line
     return line
+
+
+TP_CONTEXT = 8192
+
+
+def tp_arm(dist, rank: int, world: int, dev, steps: int, warmup: int, layers: int | None) -> dict | None:
+    """After the data-parallel measurement of a multi-GPU run: the same GPUs as ONE tensor-parallel replica
+    (batch 1, 8192 tokens of context, peer-store exchange, one CUDA graph per token), and the single-GPU step at the
+    same context for the speed-up. Returns the ``tp`` object of the JSON line on rank 0."""
+    from deltaforge_b200 import engine as E
+    from deltaforge_b200 import qwen3_5_4b_config, synth
+    from deltaforge_b200 import timeline as TL
+    from deltaforge_b200 import tp as TP
+
+    cfg = qwen3_5_4b_config() if layers is None else qwen3_5_4b_config(num_hidden_layers=layers)
+    full = synth.random_model_weights(cfg, seed=1234, device=dev, scale_dtype=torch.bfloat16)  # same seed on every rank
+    tok = torch.full((1,), 1000, dtype=torch.int64, device=dev)
+    max_seq = TP_CONTEXT + steps + warmup + 16
+
+    def timed(run) -> float:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # one GPU, same context (every rank runs it: the maximum is what a single GPU of this box does)
+    cache1 = E.DecodeCache(cfg, 1, max_seq, device=dev)
+    synth.fill_cache(cache1, TP_CONTEXT, seed=77)
+    eng1 = E.DecodeEngine(full, cache1)
+    eng1.decode(tok, warmup)
+    one_ms = timed(lambda: eng1.decode(tok, steps)) / steps
+    del eng1, cache1
+    shard = TP.shard_weights(full, rank, world)
+    del full
+    torch.cuda.empty_cache()
+    cache = E.DecodeCache(TP.shard_config(cfg, world), 1, max_seq, device=dev)
+    synth.fill_cache(cache, TP_CONTEXT, seed=77)
+    eng = TP.TensorParallelEngine(shard, cache, rank=rank, tp=world, exchange="peer")
+    eng.decode(tok, warmup)
+    tp_ms = timed(lambda: eng.decode(tok, steps, check=False)) / steps
+    eng.check_status()
+    # per-exchange cost from the kernels' own timestamps: from the last exit of the K-sharded projection to the
+    # exit of the kernel that waited for every rank's words and added them
+    trace = eng.engine.set_trace()
+    eng.decode(tok, 3)
+    torch.cuda.synchronize()
+    rows = TL.summarise(trace, [f"launch{i}" for i in range(trace.shape[0])])
+    eng.engine.set_trace(0)
+    gaps, prev_exit = [], None
+    for r in rows:
+        if r["ctas"] == -(-cfg.hidden_size // 256) and r.get("dots_done") is None and prev_exit is not None and r["exit_last"] is not None:
+            gaps.append(r["exit_last"] - prev_exit)
+        if r["exit_last"] is not None:
+            prev_exit = r["exit_last"]
+    dist.barrier()
+    if rank != 0:
+        return None
+    exchanges = 2 * cfg.num_hidden_layers
+    return {
+        "n": world,
+        "context": TP_CONTEXT,
+        "ms_per_step": tp_ms,
+        "tokens_per_s": 1e3 / tp_ms,
+        "one_gpu_ms_per_step": one_ms,
+        "speedup_vs_1gpu": one_ms / tp_ms,
+        "exchange": "peer stores from the projection's epilogue into every rank's buffer; no collective call; one CUDA graph per token",
+        "exchanges_per_token": exchanges,
+        "us_per_exchange": (sum(gaps) / len(gaps)) if gaps else None,
+        "us_per_exchange_is": "rank 0, last traced token: last exit of the K-sharded projection -> exit of the kernel that polled "
+        "every rank's words, added them in rank order and updated the residual stream",
+        "steps": steps,
+    }
 
 
 def run_tp(args) -> dict | None:
@@ -506,6 +596,7 @@ def main() -> None:
         help="cut the model to this many layers (a multiple of 4) so that a profiler capture holds little device memory; "
         "the line it prints is marked and is not a bench value",
     )
+    ap.add_argument("--no-tp-arm", action="store_true", help="with N > 1 GPUs: skip the tensor-parallel arm after the data-parallel run")
     ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
     ap.add_argument("--tp-exchange", choices=("nccl", "peer"), default="nccl", help="with --tp: how the ranks add their partial sums")
     ap.add_argument("--tp-graph", action="store_true", help="with --tp: record kernels and collectives into one CUDA graph per token")

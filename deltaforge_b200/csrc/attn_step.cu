@@ -131,7 +131,9 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   float* cl_acc = ml_s + AW * GROUPS * 2;         // [MAX_CS][GROUPS][D] per-rank sums (used in rank 0)
   float* cl_ml = cl_acc + MAX_CS * GROUPS * D;    // [MAX_CS][GROUPS][2]
   float* wgt = cl_ml + MAX_CS * GROUPS * 2;       // [GROUPS][16] merge weights
-  uint64_t* bar = (uint64_t*)(wgt + GROUPS * 16); // copy barrier
+  float* wgt_w = wgt + GROUPS * 16;               // [32] rescale weights of the warp merge and of the cluster merge
+  float* mlt_s = wgt_w + 32;                      // [GROUPS][2] merged (m, l)
+  uint64_t* bar = (uint64_t*)(mlt_s + GROUPS * 2); // copy barrier
   float* acc_s = (float*)smraw;                   // [AW][GROUPS][D], reuses the staged slice after the scan
   __shared__ int s_last;
 
@@ -251,7 +253,8 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   __syncthreads();  // everyone is done with the staged slice; its memory becomes the warp-merge buffer
   if (t == 0) trace_mark(p.trace, cta, 3);
 
-  // merge the 8 warps: afterwards thread t owns head dim t of every query head
+  // merge the 8 warps: afterwards thread t owns head dim t of every query head. The AW * GROUPS rescale weights
+  // exp(m_w - max m) are computed once, by the first warp, not by every thread.
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g) {
 #pragma unroll
@@ -262,24 +265,35 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     }
   }
   __syncthreads();
+  if (warp == 0) {  // lane = w * GROUPS + g (AW * GROUPS <= 32)
+    const int g = lane % GROUPS, w = lane / GROUPS;
+    const bool live = lane < AW * GROUPS;
+    float mg = -INFINITY;
+#pragma unroll
+    for (int ww = 0; ww < AW; ++ww) mg = fmaxf(mg, ml_s[(ww * GROUPS + g) * 2]);
+    const float mw = live ? ml_s[(w * GROUPS + g) * 2] : -INFINITY;
+    const float e = (mw == -INFINITY) ? 0.f : __expf(mw - mg);
+    float lw = live ? ml_s[(w * GROUPS + g) * 2 + 1] * e : 0.f;
+    // sum over the warps of one group in a fixed order: lanes g, g + GROUPS, g + 2 GROUPS, ...
+#pragma unroll
+    for (int o = GROUPS; o < 32; o <<= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
+    if (live) wgt_w[lane] = e;
+    if (lane < GROUPS) {
+      mlt_s[lane * 2] = mg;
+      mlt_s[lane * 2 + 1] = lw;
+    }
+  }
+  __syncthreads();
   float o[GROUPS], lt[GROUPS], mt[GROUPS];
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g) {
-    float mg = -INFINITY;
+    float og = 0.f;
 #pragma unroll
-    for (int w = 0; w < AW; ++w) mg = fmaxf(mg, ml_s[(w * GROUPS + g) * 2]);
-    float lg = 0.f, og = 0.f;
-#pragma unroll 1
-    for (int w = 0; w < AW; ++w) {
-      const float mw = ml_s[(w * GROUPS + g) * 2];
-      const float sc = (mw == -INFINITY) ? 0.f : __expf(mw - mg);
-      lg += ml_s[(w * GROUPS + g) * 2 + 1] * sc;
-      og += acc_s[(w * GROUPS + g) * D + t] * sc;
-    }
-    o[g] = og, lt[g] = lg, mt[g] = mg;
+    for (int w = 0; w < AW; ++w) og = fmaf(acc_s[(w * GROUPS + g) * D + t], wgt_w[w * GROUPS + g], og);
+    o[g] = og, lt[g] = mlt_s[g * 2 + 1], mt[g] = mlt_s[g * 2];
   }
 
-  // merge the CTAs of the cluster in rank 0
+  // merge the CTAs of the cluster in rank 0, the same way
   if (cs > 1) {
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
@@ -292,20 +306,28 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
     cluster_barrier();
     if (t == 0) trace_mark(p.trace, cta, 5);
     if (rank != 0) return;
+    if (warp == 0) {  // lane = r * GROUPS + g (cs * GROUPS <= 32)
+      const int g = lane % GROUPS, r = lane / GROUPS;
+      const bool live = lane < cs * GROUPS;
+      float mg = -INFINITY;
+      for (int rr = 0; rr < cs; ++rr) mg = fmaxf(mg, cl_ml[(rr * GROUPS + g) * 2]);
+      const float mr = live ? cl_ml[(r * GROUPS + g) * 2] : -INFINITY;
+      const float e = (mr == -INFINITY) ? 0.f : __expf(mr - mg);
+      float lr = live ? cl_ml[(r * GROUPS + g) * 2 + 1] * e : 0.f;
+#pragma unroll
+      for (int o2 = GROUPS; o2 < 32; o2 <<= 1) lr += __shfl_xor_sync(0xffffffffu, lr, o2);
+      if (live) wgt_w[lane] = e;
+      if (lane < GROUPS) {
+        mlt_s[lane * 2] = mg;
+        mlt_s[lane * 2 + 1] = lr;
+      }
+    }
+    __syncthreads();
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
-      float mg = -INFINITY;
-#pragma unroll 1
-      for (int r = 0; r < cs; ++r) mg = fmaxf(mg, cl_ml[(r * GROUPS + g) * 2]);
-      float lg = 0.f, og = 0.f;
-#pragma unroll 1
-      for (int r = 0; r < cs; ++r) {
-        const float mr = cl_ml[(r * GROUPS + g) * 2];
-        const float sc = (mr == -INFINITY) ? 0.f : __expf(mr - mg);
-        lg += cl_ml[(r * GROUPS + g) * 2 + 1] * sc;
-        og += cl_acc[(r * GROUPS + g) * D + t] * sc;
-      }
-      o[g] = og, lt[g] = lg, mt[g] = mg;
+      float og = 0.f;
+      for (int r = 0; r < cs; ++r) og = fmaf(cl_acc[(r * GROUPS + g) * D + t], wgt_w[r * GROUPS + g], og);
+      o[g] = og, lt[g] = mlt_s[g * 2 + 1], mt[g] = mlt_s[g * 2];
     }
   }
 
@@ -322,6 +344,10 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
         __stcg(&p.part_ml[ph * 2], mt[g]);
         __stcg(&p.part_ml[ph * 2 + 1], lt[g]);
       }
+    }
+    if (p.defer_merge) {  // the output projection merges the clusters' partial results while it builds its activation
+      if (t == 0) trace_mark(p.trace, cta, 6);
+      return;
     }
     __threadfence();
     __syncthreads();
@@ -380,8 +406,8 @@ template <int GROUPS>
 size_t step_smem() {
   const size_t stage = (size_t)2 * MAX_KEYS * D * 2;  // also holds the [AW][GROUPS][D] float warp-merge buffer
   const size_t merge = (size_t)AW * GROUPS * D * 4;
-  return std::max(stage, merge) + (size_t)(GROUPS * D + 2 * D + AW * GROUPS * 2 + MAX_CS * GROUPS * D + MAX_CS * GROUPS * 2 + GROUPS * 16) * 4 +
-         16 + 128;
+  return std::max(stage, merge) +
+         (size_t)(GROUPS * D + 2 * D + AW * GROUPS * 2 + MAX_CS * GROUPS * D + MAX_CS * GROUPS * 2 + GROUPS * 16 + 32 + GROUPS * 2) * 4 + 16 + 128;
 }
 
 template <int GROUPS>

@@ -100,11 +100,12 @@ struct Engine {
   PStep* ps = nullptr;    // the persistent-kernel form of the step, when the model asked for it
   unsigned long long* peer_slots[TP_MAX] = {};  // tensor parallelism by peer stores: every rank's exchange buffer
   TpPeer cur_peer = {};                          // where the next EPI_PARTIAL_PEER projection writes
+  AttnMerge cur_merge = {};                      // what the next PRO_ATTN_MERGE projection reads
   // The projections of one step in launch order, and which of them the next GEMV launch is: every kernel of
   // the batch-1 step asks the L2 for the weights of the projection `pf_dist` GEMVs ahead (0: off).
   std::vector<const dfb_linear*> order;
   int cursor = 0;
-  int pf_dist = 1;
+  int pf_dist = 0;  // measured: with programmatic dependent launch the next kernel's own copies already run ahead
   Trace trace = {};      // optional timeline buffer (dfb_engine_set_trace)
   int trace_launches = 0;
 
@@ -221,6 +222,7 @@ struct Engine {
     p.math = m.math;
     p.status = (int*)at(ws.status);
     if (epilogue == EPI_PARTIAL_PEER) p.peer = cur_peer;
+    if (prologue == PRO_ATTN_MERGE) p.merge = cur_merge;
     aim_prefetch(p.pf_ptr, p.pf_bytes, cursor + pf_dist);
     ++cursor;
     p.trace = launch_trace();
@@ -268,6 +270,35 @@ struct Engine {
     return launch_deltanet_step(d, s);
   }
 
+  // Batch 1, one GPU: when the fused attention step cuts the cache into more than one cluster of slices, the clusters'
+  // partial results are merged by the output projection while it builds its activation, not by a last-arriver
+  // protocol through global memory at the end of the attention kernel.
+  int attn_cluster_size() const {
+    int c = std::min(m.attn_splits, 4);
+    while (c < 8 && m.attn_splits / c > 16) c *= 2;
+    return c;
+  }
+  bool attn_defer_merge(const dfb_layer_desc& L) const {
+    if (m.batch != 1 || tp() || m.math != MATH_FAST || !L.out_proj.packed_k8) return false;
+    if (!attn_step_ok(m.head_dim, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) return false;
+    const int ncl = m.attn_splits / attn_cluster_size();
+    if (ncl < 2 || ncl > 16) return false;
+    GemvParams q = {};
+    q.rows = 1;
+    q.packed_k8 = (const uint32_t*)L.out_proj.packed_k8;
+    q.scale = L.out_proj.scale;
+    q.K = L.out_proj.K, q.N = L.out_proj.N, q.group = L.out_proj.group;
+    q.prologue = PRO_ATTN_MERGE;
+    q.epilogue = EPI_RESIDUAL;
+    q.math = MATH_FAST;
+    q.x = (const bf16*)at(ws.mix);
+    q.merge.acc = (const float*)at(ws.attn);
+    q.merge.ml = q.merge.acc;
+    q.merge.nclusters = ncl;
+    q.merge.d = m.head_dim;
+    return cluster_path_ok(q);
+  }
+
   int mixer_attention(const dfb_layer_desc& L, bf16* proj, long pstride, bf16* mix, bf16* qout, cudaStream_t s) {
     const int d_ = m.head_dim;
     const long kvb = (long)m.hkv * m.max_seq * d_, kvh = (long)m.max_seq * d_;
@@ -300,8 +331,7 @@ struct Engine {
       q.splits = m.attn_splits;
       // these CTAs fill an SM each: small clusters schedule sooner; the last merge takes at most 16 clusters,
       // so the longest caches of a one-KV-head shard (128 slices) use clusters of 8
-      q.cluster_size = std::min(m.attn_splits, 4);
-      while (q.cluster_size < 8 && m.attn_splits / q.cluster_size > 16) q.cluster_size *= 2;
+      q.cluster_size = attn_cluster_size();
       if (m.attn_splits > 1) {
         char* sc = at(ws.attn);
         q.part_acc = (float*)sc;
@@ -309,6 +339,19 @@ struct Engine {
         q.part_ml = (float*)sc;
         sc += align_up((size_t)m.batch * m.hq * m.attn_splits * 2 * 4, 256);
         q.counters = (unsigned*)sc;
+      }
+      q.defer_merge = attn_defer_merge(L) ? 1 : 0;
+      if (q.defer_merge) {
+        cur_merge = {};
+        cur_merge.acc = q.part_acc;
+        cur_merge.ml = q.part_ml;
+        cur_merge.nclusters = m.attn_splits / q.cluster_size;
+        cur_merge.d = d_;
+        if (m.attn_output_gate) {
+          cur_merge.gate = proj + d_;
+          cur_merge.gateh_stride = 2L * d_;
+          cur_merge.gate_swish = m.gate_is_swish;
+        }
       }
       q.out = mix;
       q.out_stride = (long)m.hq * d_;
@@ -412,7 +455,23 @@ struct Engine {
       return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_PARTIAL_PEER, (bf16*)at(ws.ar), H, nullptr, s);
     }
     if (tp()) return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
-    return gemv(L.out_proj, mix, mixw, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+    const int pro = (!dn && attn_defer_merge(L)) ? PRO_ATTN_MERGE : PRO_NONE;
+    return gemv(L.out_proj, mix, mixw, pro, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+  }
+
+  bool swiglu_in_gate_up(const dfb_layer_desc& L) const {
+    if (m.batch != 1 || tp() || m.math != MATH_FAST || !L.gate_up.packed_k8) return false;
+    GemvParams q = {};
+    q.rows = 1;
+    q.packed_k8 = (const uint32_t*)L.gate_up.packed_k8;
+    q.scale = L.gate_up.scale;
+    q.K = L.gate_up.K, q.N = L.gate_up.N, q.group = L.gate_up.group;
+    q.prologue = PRO_RMSNORM;
+    q.epilogue = EPI_SWIGLU;
+    q.math = MATH_FAST;
+    q.x = (const bf16*)at(ws.h);
+    q.norm_w = (const bf16*)L.post_norm_w;
+    return cluster_path_ok(q);
   }
 
   int second_half(int i, cudaStream_t s) {  // SwiGLU MLP
@@ -420,6 +479,12 @@ struct Engine {
     bf16* h = (bf16*)at(ws.h);
     bf16* gu = (bf16*)at(ws.gu);
     const int H = m.hidden, I = m.intermediate;
+    if (swiglu_in_gate_up(L)) {
+      // gate|up leaves bf16(silu(gate)) * up directly (a cluster holds a gate tile and the up tile of the same channels)
+      int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_SWIGLU, gu, I, nullptr, s);
+      if (rc) return rc;
+      return gemv(L.down, gu, I, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
+    }
     int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
     if (rc) return rc;
     if (peer()) {
@@ -477,12 +542,14 @@ struct Engine {
 
   int add_partial(int seg, cudaStream_t s) {
     ss_valid = false;
-    ++launches;
     if (peer()) {
       const int a = seg - 1;  // the all-reduce that ended the previous segment
+      const Trace tr = launch_trace();
+      ++launches;
       return launch_tp_reduce((bf16*)at(ws.h), peer_slots[m.tp_rank], m.tp_size, bh(), (long)(a & 1) * m.tp_size * bh(),
-                              (const unsigned*)at(ws.epoch), a, (int*)at(ws.status), s);
+                              (const unsigned*)at(ws.epoch), a, (int*)at(ws.status), tr, s);
     }
+    ++launches;
     return launch_add_partial((bf16*)at(ws.h), (const float*)at(ws.ar), (long)m.batch * m.hidden, s);
   }
 
@@ -538,6 +605,11 @@ int validate(const dfb_model_desc& m) {
   if (!m.embed || !m.final_norm_w || !m.tokens || !m.pos || !m.logits || !m.workspace || !m.inv_freq ||
       (m.num_layers && !m.layers_host)) {
     set_error("engine: null pointer in the model description");
+    return DFB_ERR_ARG;
+  }
+  if (m.tp_size > 1 && m.tp_peer_slots && 2 * m.num_layers > 254) {
+    // the exchange tag is epoch * 256 + (index of the exchange within the token), 255 being the token pick
+    set_error("engine: the peer exchange tags at most 254 exchanges per token; %d layers need %d", m.num_layers, 2 * m.num_layers);
     return DFB_ERR_ARG;
   }
   if (m.head.K != m.hidden || m.head.N != m.vocab) {

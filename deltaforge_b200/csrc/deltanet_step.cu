@@ -108,17 +108,32 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
         l2_prefetch_range(p.pf_ptr[i], p.pf_bytes[i] * (size_t)cta / nctas, p.pf_bytes[i] * (size_t)(cta + 1) / nctas);
   }
 
+  // constants of the layer (never written by a kernel): in flight before the wait
+  const float nw = col_ok ? p.norm_w[col] : 0.f;
+  const float a_log = p.a_log[hv], dt_bias = p.dt_bias[hv];
+
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (t == 0) trace_mark(p.trace, cta, 1);
-  // 2. q, k of the key head: fp32, L2-normalised, query scaled by 1/sqrt(dk).
+  // 2. Everything the projection before this kernel wrote goes in flight together (one round trip to the L2, not
+  // three): this thread's q or k element, its value and gate, and the two gate logits of the head.
   const long row = (long)b * p.row_stride;
+  const bool is_k = t >= MAX_DK;
+  const int j = is_k ? t - MAX_DK : t;
+  float x = 0.f;
+  if (j < dk) x = bf2f((is_k ? p.k : p.q)[row + (long)hk * dk + j]);
+  const float vval = col_ok ? bf2f(p.v[row + (long)hv * dv + col]) : 0.f;
+  const float zval = col_ok ? bf2f(p.z[row + (long)hv * dv + col]) : 0.f;
+  const float b_logit = bf2f(p.b[row + hv]), a_logit = bf2f(p.a[row + hv]);
+  // q, k of the key head: fp32, L2-normalised, query scaled by 1/sqrt(dk).
   {
-    const bool is_k = t >= MAX_DK;
-    const int j = is_k ? t - MAX_DK : t;
-    float x = 0.f;
-    if (j < dk) x = bf2f((is_k ? p.k : p.q)[row + (long)hk * dk + j]);
     const float ss = warp_sum(x * x);
     if (lane == 0) wred[warp] = ss;
+    if (t == DN_WARPS * 32 - 1) {  // the gates, by a thread of the last warp while the sums of squares are gathered
+      const float beta = round_bf16(sigmoid_f(b_logit));
+      const float g = __fmul_rn(-expf(a_log), softplus_f(__fadd_rn(a_logit, dt_bias)));
+      gates[0] = beta;
+      gates[1] = expf(g);
+    }
     __syncthreads();
     float tot = 0.f;
     const int w0 = is_k ? DN_WARPS / 2 : 0;
@@ -127,15 +142,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     float xn = __fmul_rn(x, rsqrt_2step(__fadd_rn(tot, 1e-6f)));
     if (!is_k) xn = __fdiv_rn(xn, sqrtf((float)dk));
     if (j < dk) (is_k ? kn : qn)[j] = xn;
-    if (t == 0) {
-      const float beta = round_bf16(sigmoid_f(bf2f(p.b[row + hv])));
-      const float g = __fmul_rn(-expf(p.a_log[hv]), softplus_f(__fadd_rn(bf2f(p.a[row + hv]), p.dt_bias[hv])));
-      gates[0] = beta;
-      gates[1] = expf(g);
-    }
   }
-  const float vval = col_ok ? bf2f(p.v[row + (long)hv * dv + col]) : 0.f;
-  const float zval = col_ok ? bf2f(p.z[row + (long)hv * dv + col]) : 0.f;
   __syncthreads();
 
   // 3. Recurrence; the updated slab goes straight back.
@@ -154,15 +161,16 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     const float ss = warp_sum(ob * ob);
     if (lane < nvb) *cluster.map_shared_rank(&cluster_ss[vb], lane) = ss;
   }
+  const float sz = silu_f(zval);  // needs nothing from the other CTAs: evaluated while their sums arrive
   cluster.sync();
   float tot = 0.f;
   for (int rk = 0; rk < nvb; ++rk) tot += cluster_ss[rk];
   if (warp == 0 && col_ok) {
     const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)dv), p.eps));
     const float nrm = round_bf16(__fmul_rn(ob, rstd));
-    float y = __fmul_rn(p.norm_w[col], nrm);
+    float y = __fmul_rn(nw, nrm);
     if (p.norm_w_bf16) y = round_bf16(y);
-    y = __fmul_rn(y, silu_f(zval));
+    y = __fmul_rn(y, sz);
     p.out[(long)b * p.out_stride + (long)hv * dv + col] = f2bf(y);
   }
   if (t == 0) trace_mark(p.trace, cta, 6);

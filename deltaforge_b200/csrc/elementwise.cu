@@ -126,7 +126,11 @@ __device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long lon
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-// Poll one exchange word until it carries `epoch`; gives up after about 0.14 s and records a code.
+// Poll one exchange word until it carries `epoch`. The limit is the seconds scale of the other bounded waits
+// (about two seconds: ordinary host skew between the ranks' launches must not trip it); a wait that runs out
+// records code 50, and once the status word is set every later wait gives up at once, so a step whose peer
+// never arrives costs one limit, not one per kernel.
+constexpr long long TP_WAIT_LIMIT_CYCLES = 4000000000LL;
 __device__ __forceinline__ bool tp_wait_word(const unsigned long long* p, unsigned epoch, float& value, int* status) {
   unsigned long long v = ld_sys_u64(p);
   if ((unsigned)(v >> 32) != epoch) {
@@ -134,7 +138,7 @@ __device__ __forceinline__ bool tp_wait_word(const unsigned long long* p, unsign
     for (;;) {
       v = ld_sys_u64(p);
       if ((unsigned)(v >> 32) == epoch) break;
-      if (clock64() - t0 > (1LL << 28)) {
+      if (clock64() - t0 > TP_WAIT_LIMIT_CYCLES || (status && *(volatile int*)status != 0)) {
         if (status) atomicCAS(status, 0, 50);
         value = 0.f;
         return false;
@@ -147,18 +151,27 @@ __device__ __forceinline__ bool tp_wait_word(const unsigned long long* p, unsign
 }
 
 __global__ void tp_reduce_kernel(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
-                                 int epoch_off, int* status) {
+                                 int epoch_off, int* status, Trace trace) {
+  // Launched with programmatic dependent launch: the projection after this kernel starts at once and streams
+  // its weights while the words from the peers are still arriving.
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_mark(trace, blockIdx.x, 0);
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  // the epoch counter was bumped by the last kernel of the previous token, long complete
   const unsigned epoch = *epoch_ctr * 256u + (unsigned)epoch_off;
   float sum = 0.f;
   bool ok = true;
-  for (int r = 0; r < tp_size; ++r) {  // rank order: every rank adds the same numbers in the same order
-    float v;
-    ok = tp_wait_word(slots + word_off + (long)r * n + i, epoch, v, status) && ok;
-    sum += v;
+  if (i < n) {
+    for (int r = 0; r < tp_size; ++r) {  // rank order: every rank adds the same numbers in the same order
+      float v;
+      ok = tp_wait_word(slots + word_off + (long)r * n + i, epoch, v, status) && ok;
+      sum += v;
+    }
   }
-  if (ok) h[i] = f2bf(__fadd_rn(bf2f(h[i]), round_bf16(sum)));
+  if (threadIdx.x == 0) trace_mark(trace, blockIdx.x, 1);
+  pdl_wait();  // the residual stream belongs to the kernels before this one
+  if (i < n && ok) h[i] = f2bf(__fadd_rn(bf2f(h[i]), round_bf16(sum)));
+  if (threadIdx.x == 0) trace_mark(trace, blockIdx.x, 6);
 }
 
 __global__ void tp_pick_kernel(const bf16* logits, int vocab_local, int batch, int tp_rank, TpPeer peer, const unsigned long long* my_slots,
@@ -187,7 +200,10 @@ __global__ void tp_pick_kernel(const bf16* logits, int vocab_local, int batch, i
     const unsigned idx = __float_as_uint(fi);
     if (v > top || (v == top && idx < pick)) top = v, pick = idx;
   }
-  if (!ok) return;
+  if (!ok) {
+    tokens[b] = -1;  // no valid pick: a token no vocabulary holds (the embedding gather reads it as a zero row)
+    return;
+  }
   tokens[b] = pick;
   if (hist) hist[(long)(*pos) * batch + b] = pick;
 }
@@ -204,7 +220,7 @@ __global__ void __launch_bounds__(128) embed_kernel(const bf16* table, const int
   const int64_t tok = tokens[b];
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const bf16 v = table[tok * hidden + i];
+    const bf16 v = tok >= 0 ? table[tok * hidden + i] : f2bf(0.f);  // negative: the mark of a failed token pick
     out[(long)b * hidden + i] = v;
     ss = fmaf(bf2f(v), bf2f(v), ss);
   }
@@ -343,9 +359,14 @@ int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s) {
 }
 
 int launch_tp_reduce(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
-                     int epoch_off, int* status, cudaStream_t s) {
+                     int epoch_off, int* status, const Trace& trace, cudaStream_t s) {
   if (n <= 0) return 0;
-  tp_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(h, slots, tp_size, n, word_off, epoch_ctr, epoch_off, status);
+  const cudaError_t e = launch_pdl(tp_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, h, slots, tp_size, n, word_off,
+                                   epoch_ctr, epoch_off, status, trace);
+  if (e != cudaSuccess) {
+    set_error("tp_reduce: launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
   return check_launch("tp_reduce");
 }
 

@@ -51,6 +51,32 @@ __device__ __forceinline__ float prologue_apply(int prologue, float xv, float wv
   return xv;
 }
 
+// PRO_ATTN_MERGE: the four activation values k .. k+3 (k a multiple of 4) of the gated attention output.
+__device__ __forceinline__ void attn_merge_values(const AttnMerge& a, int k, float (&v)[4]) {
+  const int h = k / a.d, i = k % a.d;
+  const float* ml = a.ml + (long)h * a.nclusters * 2;
+  float mg = -INFINITY;
+  for (int c = 0; c < a.nclusters; ++c) mg = fmaxf(mg, __ldcg(ml + 2 * c));
+  float o[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+  for (int c = 0; c < a.nclusters; ++c) {  // fixed order: the same bits every run
+    const float m = __ldcg(ml + 2 * c);
+    const float w = (m == -INFINITY) ? 0.f : __expf(m - mg);
+    l = fmaf(w, __ldcg(ml + 2 * c + 1), l);
+    const float4 pa = __ldcg((const float4*)(a.acc + ((long)h * a.nclusters + c) * a.d + i));
+    o[0] = fmaf(w, pa.x, o[0]), o[1] = fmaf(w, pa.y, o[1]), o[2] = fmaf(w, pa.z, o[2]), o[3] = fmaf(w, pa.w, o[3]);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float y = round_bf16(o[j] / l);
+    if (a.gate) {
+      const float gv = bf2f(a.gate[(long)h * a.gateh_stride + i + j]);
+      const float gg = round_bf16(a.gate_swish ? silu_f(gv) : sigmoid_f(gv));
+      y = round_bf16(__fmul_rn(y, gg));
+    }
+    v[j] = y;
+  }
+}
+
 __device__ __forceinline__ float load_scale(const GemvParams& p, long idx) {
   return p.scale_bf16 ? bf2f(((const bf16*)p.scale)[idx]) : ((const float*)p.scale)[idx];
 }

@@ -415,6 +415,11 @@ int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   static OncePerDevice once;
   const int configured = once.run(gemv_configure);
   if (configured) return configured;
+  if ((p.epilogue == EPI_SWIGLU || p.prologue == PRO_ATTN_MERGE) && !(!p.force_tiled && p.status && p.N < 65536 && cluster_path_ok(p))) {
+    set_error("int4 gemv: the SwiGLU epilogue and the attention-merge prologue exist in the cluster kernel only (one row, "
+              "re-packed group-128 weight; SwiGLU: N a multiple of two tiles)");
+    return 2;
+  }
   // eight rows and more: the weight tile is shared by enough rows for the tensor cores
   if (!p.force_tiled && p.rows >= 8 && tc_path_ok(p)) return launch_gemm_tc(p, p.status, stream);
   if (!p.force_tiled && p.status) {

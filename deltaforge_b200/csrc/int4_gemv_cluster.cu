@@ -33,8 +33,6 @@ namespace dfb {
 
 namespace {
 
-constexpr int CTHREADS = 256;  // consumer threads
-constexpr int THREADS = CTHREADS + 32;
 constexpr int UROWS = 16;      // word rows per unit = one 128-row scale group
 constexpr int MAX_CS = 8;      // portable cluster size limit
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -71,7 +69,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
       : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CTHREADS) : "memory"); }
+template <int CT>
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -111,84 +115,115 @@ __device__ __forceinline__ void finish_tile(const GemvParams& p, int tile, int t
     for (int w = 0; w < TNW / 32; ++w) tot += wred[w];
     p.ss_out[tile] = tot;
   }
+  asm volatile("bar.sync 2, %0;" ::"n"(TNW) : "memory");  // wred is written again by the next tile of this CTA
 }
 
 struct ClusterArgs {
   GemvParams p;
-  int cs;        // cluster size = CTAs per column tile
-  int max_units; // most groups any CTA of a cluster gets
+  int cs;         // cluster size = CTAs that share the rows of a column tile
+  int max_units;  // most groups any CTA of a cluster gets
+  int tpc;        // column tiles a cluster works through, one after the other
+  int num_tiles;  // ceil(N / TNW)
+  int stages;     // ring depth in units (>= max_units when tpc == 1: nothing is recycled then)
   int* status;
 };
 
-template <int TNW>
-__global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_constant__ CUtensorMap wmap,
-                                                               const __grid_constant__ CUtensorMap smap, const ClusterArgs a) {
+constexpr int MAX_TPC = 4;
+
+// TNW: columns per tile. CW: consumer warps (8 or 16); one more warp issues the copies.
+template <int TNW, int CW>
+__global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid_constant__ CUtensorMap wmap,
+                                                                    const __grid_constant__ CUtensorMap smap, const ClusterArgs a) {
+  constexpr int CT = CW * 32;          // consumer threads
   constexpr int CQ = TNW / 4;          // column quads per tile
-  constexpr int RL = CTHREADS / CQ;    // row lanes
+  constexpr int RL = CT / CQ;          // row lanes
   constexpr int RPT = UROWS / RL;      // word rows per thread per unit
+  static_assert(RL >= 1 && RPT >= 1 && RL * RPT == UROWS, "thread layout must tile a unit");
   constexpr int W_BYTES = UROWS * TNW * 4;
   constexpr int STAGE = W_BYTES + TNW * 4;  // + one scale row (fp32 size; bf16 uses half of it)
   extern __shared__ unsigned char smem_raw[];
   const GemvParams& p = a.p;
   const int G = p.K / 128;
-  unsigned char* stage0 = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // max_units * STAGE
-  unsigned char* xq = stage0 + (size_t)a.max_units * STAGE;        // [max_units*16][16] activation bytes for dp4a
+  unsigned char* ring = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // stages * STAGE
+  unsigned char* xq = ring + (size_t)a.stages * STAGE;             // [max_units*16][16] activation bytes for dp4a
   int* mk = (int*)(xq + (size_t)a.max_units * UROWS * 16);         // [max_units*16] sum of m per word row
   float* fg = (float*)(mk + a.max_units * UROWS);                  // [max_units] 2^e per group
   float* red = fg + ((a.max_units + 3) & ~3);                      // [RL][TNW] row-lane partials
-  float* dsm = red + RL * TNW;                                     // [cs][TNW] column sums from every rank (used in rank 0)
-  uint64_t* full = (uint64_t*)(dsm + MAX_CS * TNW);                // [max_units]
-  float* wred = (float*)(full + a.max_units);                      // [8]
+  float* dsm = red + RL * TNW;                                     // [tpc][cs][TNW] column sums from every rank (used in rank 0)
+  uint64_t* full = (uint64_t*)(dsm + a.tpc * a.cs * TNW);          // [stages]
+  uint64_t* empty = full + a.stages;                               // [stages]
+  float* wred = (float*)(empty + a.stages);                        // [16]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const int cs = a.cs;
   const int rank = (int)cluster_rank();
-  const int tile = blockIdx.x / cs;
+  const int cluster = blockIdx.x / cs;
+  // A cluster's tiles are neighbours, except under the SwiGLU epilogue, where they are a tile of gate_proj columns
+  // and the tile of up_proj columns of the same channels (half the matrix further on).
+  const bool swiglu = p.epilogue == EPI_SWIGLU;
+  const int tile_step = swiglu ? a.num_tiles / 2 : 1;
+  const int tile0 = swiglu ? cluster : cluster * a.tpc;
+  const int ntiles = swiglu ? 2 : min(a.tpc, a.num_tiles - tile0);  // >= 1: the grid holds no empty cluster
   const int g0 = (int)((long)rank * G / cs), g1 = (int)((long)(rank + 1) * G / cs);
   const int nunits = g1 - g0;
+  const int total = ntiles * nunits;
   const uint32_t scale_bytes = p.scale_bf16 ? TNW * 2 : TNW * 4;
   const int cta = blockIdx.x;
 
   if (t == 0) {
     trace_mark(p.trace, cta, 0);
-    for (int s = 0; s < nunits; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CW);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   bool ok = true;
-  EpiPre pre = {};
-  if (warp == CTHREADS / 32) {
-    // producer: everything this CTA will read from the weight, at once (weights never depend on earlier kernels)
+  EpiPre pre = {};  // epilogue inputs of the cluster's first tile (later tiles of a folded grid load theirs at the end)
+  if (warp == CW) {
+    // producer: the weights never depend on earlier kernels, so the ring is filled at once; units beyond the
+    // ring's depth (several tiles per cluster) follow as the consumers hand stages back
     if (lane == 0) {
       const uint64_t pol = make_evict_first_policy();
-      for (int s = 0; s < nunits; ++s) {
-        unsigned char* dst = stage0 + (size_t)s * STAGE;
-        mbar_expect_tx(&full[s], W_BYTES + scale_bytes);
-        tma_load_2d(dst, &wmap, tile * TNW, (g0 + s) * UROWS, &full[s], pol);
-        tma_load_2d(dst + W_BYTES, &smap, tile * TNW, g0 + s, &full[s], pol);
-      }
-      // with this CTA's own loads queued, start the L2 on a slice of what the next GEMV of the step will read
+      int st = 0, round = 0, i = 0, s = 0;
+      for (int j = 0; j < total; ++j) {
+        if (round > 0 && !mbar_wait(&empty[st], (round - 1) & 1)) {
+          atomicExch(a.status, 6);
+          break;
+        }
+        unsigned char* dst = ring + (size_t)st * STAGE;
+        mbar_expect_tx(&full[st], W_BYTES + scale_bytes);
+        tma_load_2d(dst, &wmap, (tile0 + i * tile_step) * TNW, (g0 + s) * UROWS, &full[st], pol);
+        tma_load_2d(dst + W_BYTES, &smap, (tile0 + i * tile_step) * TNW, g0 + s, &full[st], pol);
+        if (++s == nunits) s = 0, ++i;
+        if (++st == a.stages) st = 0, ++round;
+        if (j + 1 == min(total, a.stages)) {
+          // with this CTA's first copies queued, start the L2 on a slice of what a later GEMV of the step will read
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
-        if (p.pf_ptr[i] != nullptr)
-          l2_prefetch_range(p.pf_ptr[i], p.pf_bytes[i] * (size_t)cta / gridDim.x, p.pf_bytes[i] * (size_t)(cta + 1) / gridDim.x);
-      trace_mark(p.trace, cta, 7);
+          for (int q = 0; q < 2; ++q)
+            if (p.pf_ptr[q] != nullptr)
+              l2_prefetch_range(p.pf_ptr[q], p.pf_bytes[q] * (size_t)cta / gridDim.x, p.pf_bytes[q] * (size_t)(cta + 1) / gridDim.x);
+          trace_mark(p.trace, cta, 7);
+        }
+      }
     }
+    __syncwarp();  // the whole warp takes part in the (aligned) cluster barrier below
   } else {
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
     if (t == 0) trace_mark(p.trace, cta, 1);
     // Everything this CTA reads that an earlier kernel wrote goes in flight at once: the activation values of
-    // the first group each warp quantises, and what the epilogue adds to (rank 0 finishes the tile).
+    // the first group each warp quantises, and what the epilogue adds to (rank 0 finishes the tiles).
     uint2 xraw = make_uint2(0u, 0u), wraw = make_uint2(0u, 0u);
-    if (warp < nunits) {
+    if (warp < nunits && p.prologue != PRO_ATTN_MERGE) {
       const int k = (g0 + warp) * 128 + lane * 4;
       xraw = *(const uint2*)(p.x + k);
       if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
       if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
     }
-    if ((cs == 1 || rank == 0) && t < TNW && tile * TNW + t < p.N) pre = epilogue_preload(p, 0, tile * TNW + t);
+    if ((cs == 1 || rank == 0) && t < TNW && tile0 * TNW + t < p.N) pre = epilogue_preload(p, 0, tile0 * TNW + t);
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
       float tot = 0.f;
@@ -196,24 +231,24 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
         for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
       } else {
         float ss = 0.f;
-        for (int k = t; k < p.K; k += CTHREADS) {
+        for (int k = t; k < p.K; k += CT) {
           const float v = bf2f(p.x[k]);
           ss = fmaf(v, v, ss);
         }
         ss = warp_sum(ss);
         if (lane == 0) wred[warp] = ss;
-        consumer_sync();
+        consumer_sync<CT>();
 #pragma unroll
-        for (int w = 0; w < CTHREADS / 32; ++w) tot += wred[w];
+        for (int w = 0; w < CW; ++w) tot += wred[w];
       }
       rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
     }
     // one warp per group of this CTA: shared exponent, 16-bit integers, bytes laid out for dp4a
-    for (int gl = warp; gl < nunits; gl += CTHREADS / 32) {
+    for (int gl = warp; gl < nunits; gl += CW) {
       const int g = g0 + gl;
       float v[4];
       float amax = 0.f;
-      if (gl != warp) {  // later groups of this warp (the first one's values are already here)
+      if (gl != warp && p.prologue != PRO_ATTN_MERGE) {  // later groups of this warp (the first one's values are already here)
         const int k = g * 128 + lane * 4;
         xraw = *(const uint2*)(p.x + k);
         if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
@@ -223,11 +258,14 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
                            __uint_as_float(xraw.y & 0xffff0000u)};
       const float wr[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u), __uint_as_float(wraw.y << 16),
                            __uint_as_float(wraw.y & 0xffff0000u)};
+      if (p.prologue == PRO_ATTN_MERGE) {
+        attn_merge_values(p.merge, g * 128 + lane * 4, v);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
-        amax = fmaxf(amax, fabsf(v[i]));
+        for (int i = 0; i < 4; ++i) v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
       amax = warp_max(amax);
       int E = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
       E = max(E, -100);
@@ -246,76 +284,106 @@ __global__ void __launch_bounds__(THREADS) gemv_cluster_kernel(const __grid_cons
       msum += __shfl_xor_sync(0xffffffffu, msum, 1);  // lanes 2j, 2j+1 share word row j of the group
       if ((lane & 1) == 0) mk[gl * UROWS + (lane >> 1)] = msum;
     }
-    consumer_sync();
+    consumer_sync<CT>();
     if (t == 0) trace_mark(p.trace, cta, 2);
 
     const int rl = t / CQ, cq = t % CQ;
-    float tot[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < nunits; ++s) {
-      if (ok) ok = mbar_wait(&full[s], 0);
-      if (!ok) continue;
-      const unsigned char* wbase = stage0 + (size_t)s * STAGE;
-      int acc_h[4] = {0, 0, 0, 0}, acc_l[4] = {0, 0, 0, 0};
-      int msum = 0;
+    int st = 0, phase = 0;
+    for (int i = 0; i < ntiles; ++i) {
+      float tot[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < nunits; ++s) {
+        if (ok) ok = mbar_wait(&full[st], phase);
+        if (ok) {
+          const unsigned char* wbase = ring + (size_t)st * STAGE;
+          // even rows of a word sit in the low nibbles of its bytes, odd rows in the high nibbles: the odd rows are
+          // used where they are (16 x their value) in accumulators of their own, and shifted once per group
+          int acc_eh[4] = {0, 0, 0, 0}, acc_el[4] = {0, 0, 0, 0}, acc_oh[4] = {0, 0, 0, 0}, acc_ol[4] = {0, 0, 0, 0};
+          int msum = 0;
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int kb = rl + RL * i;
-        const uint4 xw = *(const uint4*)(xq + (s * UROWS + kb) * 16);
-        const uint4 w4 = *(const uint4*)(wbase + kb * (TNW * 4) + cq * 16);
-        msum += mk[s * UROWS + kb];
-        const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+          for (int r = 0; r < RPT; ++r) {
+            const int kb = rl + RL * r;
+            const uint4 xw = *(const uint4*)(xq + (s * UROWS + kb) * 16);
+            const uint4 w4 = *(const uint4*)(wbase + kb * (TNW * 4) + cq * 16);
+            msum += mk[s * UROWS + kb];
+            const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t ne = wv[q] & 0x0F0F0F0Fu, no = (wv[q] >> 4) & 0x0F0F0F0Fu;
-          acc_h[q] = dp4a_us(ne, xw.x, acc_h[q]);
-          acc_h[q] = dp4a_us(no, xw.y, acc_h[q]);
-          acc_l[q] = dp4a_uu(ne, xw.z, acc_l[q]);
-          acc_l[q] = dp4a_uu(no, xw.w, acc_l[q]);
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t ne = wv[q] & 0x0F0F0F0Fu, no = wv[q] & 0xF0F0F0F0u;
+              acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
+              acc_oh[q] = dp4a_us(no, xw.y, acc_oh[q]);
+              acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
+              acc_ol[q] = dp4a_uu(no, xw.w, acc_ol[q]);
+            }
+          }
+          float sc[4];
+          if (p.scale_bf16) {
+            const uint2 v = *(const uint2*)(wbase + W_BYTES + cq * 8);
+            sc[0] = __uint_as_float(v.x << 16), sc[1] = __uint_as_float(v.x & 0xffff0000u);
+            sc[2] = __uint_as_float(v.y << 16), sc[3] = __uint_as_float(v.y & 0xffff0000u);
+          } else {
+            const float4 v = *(const float4*)(wbase + W_BYTES + cq * 16);
+            sc[0] = v.x, sc[1] = v.y, sc[2] = v.z, sc[3] = v.w;
+          }
+          const float f = fg[s];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            // sum over this thread's rows of (nibble - 8) * m, exact: the odd-row part is a multiple of 16
+            const int S = (acc_eh[q] * 256 + acc_el[q]) + ((acc_oh[q] * 256 + acc_ol[q]) >> 4) - 8 * msum;
+            tot[q] = fmaf((float)S * f, sc[q], tot[q]);
+          }
+          if (a.stages < total) {  // the stage goes back to the producer (only when units outnumber stages)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
+          }
         }
+        if (++st == a.stages) st = 0, phase ^= 1;
       }
-      float sc[4];
-      if (p.scale_bf16) {
-        const uint2 v = *(const uint2*)(wbase + W_BYTES + cq * 8);
-        sc[0] = __uint_as_float(v.x << 16), sc[1] = __uint_as_float(v.x & 0xffff0000u);
-        sc[2] = __uint_as_float(v.y << 16), sc[3] = __uint_as_float(v.y & 0xffff0000u);
-      } else {
-        const float4 v = *(const float4*)(wbase + W_BYTES + cq * 16);
-        sc[0] = v.x, sc[1] = v.y, sc[2] = v.z, sc[3] = v.w;
-      }
-      const float f = fg[s];
+      if (t == 0 && i + 1 == ntiles) trace_mark(p.trace, cta, 3);
+      // add the row lanes, then hand this CTA's column sums to rank 0
+      if (i > 0) consumer_sync<CT>();  // the previous tile's row-lane sums have been read
+      *(float4*)(red + rl * TNW + cq * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+      consumer_sync<CT>();
+      if (t == 0 && i + 1 == ntiles) trace_mark(p.trace, cta, 4);
+      if (t < TNW) {
+        float v = 0.f;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int S = acc_h[q] * 256 + acc_l[q] - 8 * msum;  // sum over this thread's rows of (nibble - 8) * m
-        tot[q] = fmaf((float)S * f, sc[q], tot[q]);
+        for (int r = 0; r < RL; ++r) v += red[r * TNW + t];
+        if (cs == 1 && !swiglu) {
+          if (i > 0 && (tile0 + i) * TNW + t < p.N) pre = epilogue_preload(p, 0, (tile0 + i) * TNW + t);
+          finish_tile<TNW>(p, tile0 + i, t, v, wred, pre);
+        } else {
+          dsmem_store(dsm + (i * cs + rank) * TNW + t, 0, v);
+        }
       }
     }
     if (!ok && lane == 0) atomicExch(a.status, 4);
-    if (t == 0) trace_mark(p.trace, cta, 3);
-    // add the row lanes, then hand this CTA's column sums to rank 0
-    *(float4*)(red + rl * TNW + cq * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
-    consumer_sync();
-    if (t == 0) trace_mark(p.trace, cta, 4);
-    if (t < TNW) {
-      float v = 0.f;
-#pragma unroll
-      for (int r = 0; r < RL; ++r) v += red[r * TNW + t];
-      if (cs == 1) {
-        finish_tile<TNW>(p, tile, t, v, wred, pre);
-      } else {
-        dsmem_store(dsm + rank * TNW + t, 0, v);
-      }
-    }
   }
-  if (cs == 1) {
+  if (cs == 1 && !swiglu) {
     if (t == 0) trace_mark(p.trace, cta, 6);
     return;
   }
-  cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
+  if (cs > 1) cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
+  else __syncthreads();
   if (t == 0) trace_mark(p.trace, cta, 5);
-  if (rank == 0 && t < TNW) {
-    float v = 0.f;
-    for (int r = 0; r < cs; ++r) v += dsm[r * TNW + t];
-    finish_tile<TNW>(p, tile, t, v, wred, pre);
+  if (swiglu) {
+    // rank 0 holds the gate_proj and the up_proj sums of the same TNW channels: bf16(silu(g)) * u, rounded as the
+    // reference's SwiGLUMLP rounds it (src/deltaforge/reference.py:692-693, src/deltaforge/kernels/fused_swiglu.py:18-22)
+    if (rank == 0 && t < TNW && tile0 * TNW + t < p.N / 2) {
+      float g = 0.f, u = 0.f;
+      for (int r = 0; r < cs; ++r) {
+        g += dsm[r * TNW + t];
+        u += dsm[(cs + r) * TNW + t];
+      }
+      const float sv = round_bf16(silu_f(round_bf16(g)));
+      p.out[tile0 * TNW + t] = f2bf(__fmul_rn(sv, round_bf16(u)));
+    }
+  } else if (rank == 0 && t < TNW) {
+    for (int i = 0; i < ntiles; ++i) {
+      float v = 0.f;
+      for (int r = 0; r < cs; ++r) v += dsm[(i * cs + r) * TNW + t];
+      if (i > 0 && (tile0 + i) * TNW + t < p.N) pre = epilogue_preload(p, 0, (tile0 + i) * TNW + t);
+      finish_tile<TNW>(p, tile0 + i, t, v, wred, pre);
+    }
   }
   if (t == 0) trace_mark(p.trace, cta, 6);
 }
@@ -341,16 +409,76 @@ int pick_cs(int K) {
   // Measured on B200: with K = 2560 (20 groups) clusters of 4 with 5 groups per CTA beat clusters of 8
   // (fewer CTAs repeat the prologue, smaller clusters are scheduled sooner); the deeper matrices
   // (K = 4096, 9216) need 8 CTAs per tile to keep a CTA's units within shared memory and the SMs busy.
-  if (G <= 24) return std::max(1, G / 5);
+  if (G <= 24) return std::max(1, std::min(MAX_CS, (G + 2) / 5));
   return MAX_CS;
 }
 
+// How a GEMV is cut: clusters of `cs` CTAs share the rows of a tile; a grid that would not be resident in one
+// go (more CTAs than about one and a half per SM: its second wave would start only when the first leaves) is
+// folded so that every cluster works through `tpc` tiles, its CTAs recycling a ring of `stages` units.
+struct ClusterPlan {
+  int cs, max_units, tiles, tpc, clusters, stages, cw;
+  size_t smem;
+};
+
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : fallback;
+}
+
 template <int TNW>
-size_t cluster_smem(int max_units) {
-  constexpr int RL = CTHREADS / (TNW / 4);
+ClusterPlan plan_cluster(int K, int N, bool swiglu) {
+  ClusterPlan c = {};
+  const int G = K / 128;
+  c.cs = pick_cs(K);
+  c.max_units = (G + c.cs - 1) / c.cs;
+  c.tiles = (N + TNW - 1) / TNW;
+  c.cw = env_int("DFB_CW", 16);
+  const int sms = 148;
+  const int ctas = c.tiles * c.cs;
+  c.tpc = ctas > env_int("DFB_FOLD_ABOVE", 222) ? std::min(MAX_TPC, (ctas + sms - 1) / sms) : 1;
+  if (swiglu) c.tpc = 2;  // a gate tile and its up tile per cluster
+  c.clusters = (c.tiles + c.tpc - 1) / c.tpc;
   const size_t stage = (size_t)UROWS * TNW * 4 + TNW * 4;
-  return (size_t)max_units * stage + (size_t)max_units * UROWS * 16 + (size_t)max_units * UROWS * 4 +
-         (size_t)((max_units + 3) & ~3) * 4 + (size_t)RL * TNW * 4 + (size_t)MAX_CS * TNW * 4 + (size_t)max_units * 8 + 32 + 128;
+  c.stages = c.max_units;
+  if (c.tpc > 1) c.stages = std::min(c.tpc * c.max_units, std::max(c.max_units, (int)(((size_t)env_int("DFB_RING_KB", 108) << 10) / stage)));
+  const int rl = c.cw * 32 / (TNW / 4);
+  c.smem = (size_t)c.stages * stage + (size_t)c.max_units * UROWS * 16 + (size_t)c.max_units * UROWS * 4 +
+           (size_t)((c.max_units + 3) & ~3) * 4 + (size_t)rl * TNW * 4 + (size_t)c.tpc * c.cs * TNW * 4 + (size_t)c.stages * 16 + 64 + 128;
+  return c;
+}
+
+template <int TNW, int CW>
+int launch_cluster_cfg(const GemvParams& p, const ClusterPlan& c, const CUtensorMap& wmap, const CUtensorMap& smap, int* status,
+                       cudaStream_t stream) {
+  ClusterArgs a = {};
+  a.p = p;
+  a.cs = c.cs;
+  a.max_units = c.max_units;
+  a.tpc = c.tpc;
+  a.num_tiles = c.tiles;
+  a.stages = c.stages;
+  a.status = status;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(c.clusters * c.cs, 1, 1);
+  cfg.blockDim = dim3(CW * 32 + 32, 1, 1);
+  cfg.dynamicSmemBytes = c.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = c.cs;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW, CW>, wmap, smap, a);
+  if (e != cudaSuccess) {
+    set_error("int4 gemv (cluster): launch failed: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return check_launch("int4 gemv (cluster)");
 }
 
 template <int TNW>
@@ -388,34 +516,9 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
       return 1;
     }
   }
-  ClusterArgs a = {};
-  a.p = p;
-  a.cs = pick_cs(p.K);
-  const int G = p.K / 128;
-  a.max_units = (G + a.cs - 1) / a.cs;
-  a.status = status;
-  const int tiles = (p.N + TNW - 1) / TNW;
-  const size_t smem = cluster_smem<TNW>(a.max_units);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles * a.cs, 1, 1);
-  cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = a.cs;
-  attr[1].val.clusterDim.y = 1;
-  attr[1].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW>, wmap, smap, a);
-  if (e != cudaSuccess) {
-    set_error("int4 gemv (cluster): launch failed: %s", cudaGetErrorString(e));
-    return 1;
-  }
-  return check_launch("int4 gemv (cluster)");
+  const ClusterPlan c = plan_cluster<TNW>(p.K, p.N, p.epilogue == EPI_SWIGLU);
+  if (c.cw == 8) return launch_cluster_cfg<TNW, 8>(p, c, wmap, smap, status, stream);
+  return launch_cluster_cfg<TNW, 16>(p, c, wmap, smap, status, stream);
 }
 
 }  // namespace
@@ -423,22 +526,31 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
 // Shapes the cluster kernel takes: the same preconditions as the streaming kernel, N a multiple of 4
 // for 16-byte rows, and a per-CTA footprint that leaves room for several CTAs per SM.
 bool cluster_path_ok(const GemvParams& p) {
-  if (!(p.rows == 1 && p.packed_k8 != nullptr && p.group == 128 && p.K % 256 == 0 && p.N % 4 == 0 &&
+  if (!(p.rows == 1 && p.packed_k8 != nullptr && p.group == 128 && p.K % 128 == 0 && p.N % 4 == 0 &&
         ((uintptr_t)p.packed_k8 % 16) == 0 && ((uintptr_t)p.scale % 16) == 0 && p.math == MATH_FAST &&
         ((uintptr_t)p.x % 8) == 0 && (p.prologue != PRO_RMSNORM || ((uintptr_t)p.norm_w % 8) == 0) &&
-        (p.prologue != PRO_SILU_MUL || ((uintptr_t)p.up % 8) == 0)))
+        (p.prologue != PRO_SILU_MUL || ((uintptr_t)p.up % 8) == 0) &&
+        (p.prologue != PRO_ATTN_MERGE || (p.merge.acc && p.merge.ml && p.merge.nclusters >= 1 && p.merge.nclusters <= 16 &&
+                                          p.merge.d % 128 == 0 && p.K % p.merge.d == 0 && ((uintptr_t)p.merge.acc % 16) == 0))))
     return false;
-  const int cs = pick_cs(p.K), G = p.K / 128;
-  const int max_units = (G + cs - 1) / cs;
-  const size_t smem = p.N >= 4096 ? cluster_smem<256>(max_units) : cluster_smem<128>(max_units);
-  return smem <= 100 * 1024;  // at least two CTAs per SM
+  const bool swiglu = p.epilogue == EPI_SWIGLU;
+  const int tnw = cluster_tile_width(p.N);
+  if (swiglu && (p.N % (2 * tnw) != 0)) return false;  // whole tiles of gate columns, then whole tiles of up columns
+  const ClusterPlan c = tnw == 256 ? plan_cluster<256>(p.K, p.N, swiglu) : plan_cluster<128>(p.K, p.N, swiglu);
+  // one tile per cluster: small enough for two CTAs per SM; folded grids run one CTA per SM with a deeper ring
+  return c.smem <= (size_t)(c.tpc == 1 ? 104 : 132) * 1024;
 }
 
 int cluster_configure() {
-  cudaError_t e = cudaFuncSetAttribute(gemv_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  if (e == cudaSuccess) e = prefer_max_shared(gemv_cluster_kernel<256>);
-  if (e == cudaSuccess) e = prefer_max_shared(gemv_cluster_kernel<128>);
+  cudaError_t e = cudaSuccess;
+  auto opt_in = [&e](auto kernel) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess) e = prefer_max_shared(kernel);
+  };
+  opt_in(gemv_cluster_kernel<256, 8>);
+  opt_in(gemv_cluster_kernel<256, 16>);
+  opt_in(gemv_cluster_kernel<128, 8>);
+  opt_in(gemv_cluster_kernel<128, 16>);
   if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
   return 0;
 }

@@ -18,11 +18,28 @@ struct Trace {
   int ctas;  // CTAs recorded per launch
 };
 
-enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
+// PRO_ATTN_MERGE (engine-internal, cluster kernel only): the activation is the gated attention output, formed on the
+// fly from the partial results the split-KV attention step left per slice cluster (see AttnMerge)
+enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2, PRO_ATTN_MERGE = 3 };
+
+// The last step of split-KV attention, done by its consumer: head h's output is sum_c w_c acc[h][c][:] / sum_c w_c l[h][c]
+// with w_c = exp(m[h][c] - max_c m[h][c]), rounded to bf16, then multiplied by the bf16 output gate
+// (src/deltaforge/reference.py:558-568, :675-676). acc [heads, nclusters, d] fp32, ml [heads, nclusters, 2] = (m, l).
+struct AttnMerge {
+  const float* acc;
+  const float* ml;
+  int nclusters;  // 2..16
+  int d;          // head dim (a multiple of 128)
+  const bf16* gate;  // optional gate logits: element (h, i) at gate[h * gateh_stride + i]
+  long gateh_stride;
+  int gate_swish;
+};
 // EPI_PARTIAL_F32 (engine-internal, tensor parallelism): `out` is an fp32 buffer that receives the unrounded sum
 // EPI_PARTIAL_PEER (engine-internal): the unrounded sum goes, tagged with an epoch, straight into a slot of every
 // rank's exchange buffer (peer stores over NVLink); see TpPeer
-enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2, EPI_PARTIAL_F32 = 3, EPI_PARTIAL_PEER = 4 };
+// EPI_SWIGLU (engine-internal, cluster kernel only): the matrix is gate_proj|up_proj along N; `out` receives the N/2
+// values bf16(bf16(silu(gate)) * up) of SwiGLUMLP instead of the N projections
+enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CONV = 2, EPI_PARTIAL_F32 = 3, EPI_PARTIAL_PEER = 4, EPI_SWIGLU = 5 };
 
 // Where the K-sharded projections of a tensor-parallel rank leave their partial sums when the ranks exchange
 // them by peer stores: slots[r] is rank r's exchange buffer (8-byte words {fp32 bits, epoch}); this rank
@@ -84,6 +101,7 @@ struct GemvParams {
   const void* pf_ptr[2];
   size_t pf_bytes[2];
   Trace trace;
+  AttnMerge merge;  // PRO_ATTN_MERGE only
 };
 
 // Bytes of scratch the split-K path needs for a problem, and the number of counters.
@@ -216,6 +234,10 @@ struct AttnStepParams {  // prep + split-KV decode + merge + gate in one launch 
   bf16* out;  // [batch, hq*d]
   long out_stride;
   int* status;  // device word set if the bounded wait on the staging copies gives up
+  // 1: with more than one cluster of slices per KV head, leave the per-cluster partial results (part_acc, part_ml) for the
+  // consumer to merge (PRO_ATTN_MERGE of the output projection) instead of merging them here by the last cluster to arrive;
+  // `out` is then not written and `counters` not used
+  int defer_merge;
   const void* pf_ptr[2];  // as in GemvParams
   size_t pf_bytes[2];
   Trace trace;
@@ -252,7 +274,7 @@ int launch_add_partial(bf16* h, const float* sum, long n, cudaStream_t s);
 // The receiving side of the peer exchange: wait (bounded) for the tp words of every element to carry the epoch,
 // add them in rank order, round to bf16 and add to the residual stream. slots: this rank's own buffer.
 int launch_tp_reduce(bf16* h, const unsigned long long* slots, int tp_size, long n, long word_off, const unsigned* epoch_ctr,
-                     int epoch_off, int* status, cudaStream_t s);
+                     int epoch_off, int* status, const Trace& trace, cudaStream_t s);
 // Greedy pick across vocabulary shards by peer exchange of (best logit, global index); tokens holds the local index on entry.
 int launch_tp_pick(const bf16* logits, int vocab_local, int batch, int tp_rank, const TpPeer& peer, const unsigned long long* my_slots,
                    int64_t* tokens, int64_t* hist, const int* pos, int* status, cudaStream_t s);

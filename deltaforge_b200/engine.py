@@ -293,7 +293,7 @@ class DecodeEngine:
                 raise ValueError("quantised weights must be contiguous")
             k, n = qw.in_features, qw.out_features
             # the re-packed copy serves the batch-1 streaming kernels and the tensor-core product (8 rows and more)
-            wants_k8 = (self.batch == 1 and k % 256 == 0) or (self.batch >= 8 and k % 128 == 0)
+            wants_k8 = k % 128 == 0 and (self.batch == 1 or self.batch >= 8)
             if qw.k8 is None and not persistent and wants_k8 and qw.group_size == 128 and n % 4 == 0:
                 from . import ops  # the re-packed copy the streaming GEMV reads; made once per weight
 

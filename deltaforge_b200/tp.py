@@ -31,7 +31,7 @@ from torch import Tensor
 from . import _lib
 from .config import LINEAR_ATTENTION
 from .engine import DecodeCache, DecodeEngine, LayerWeights, ModelWeights
-from .quant import QuantisedWeight, group_size_for
+from .quant import QuantisedWeight
 
 BF16 = torch.bfloat16
 
@@ -41,10 +41,23 @@ BF16 = torch.bfloat16
 # --------------------------------------------------------------------------------------
 
 
+def kv_heads_per_rank(cfg, tp: int) -> int:
+    """KV heads a rank holds: its share, or one replicated head when there are more ranks than KV heads."""
+    hkv = cfg.num_key_value_heads
+    if hkv % tp == 0:
+        return hkv // tp
+    if tp % hkv == 0 and (cfg.num_attention_heads // hkv) % (cfg.num_attention_heads // tp) == 0:
+        return 1  # tp / hkv consecutive ranks share one KV head; each takes some of its query heads
+    raise ValueError(f"num_key_value_heads = {hkv} neither divides over nor is replicated evenly across {tp} ranks")
+
+
 def shard_config(cfg, tp: int):
-    """The model configuration one of ``tp`` ranks sees: its share of heads, MLP channels and vocabulary."""
-    for name in ("num_attention_heads", "num_key_value_heads", "linear_num_key_heads", "linear_num_value_heads",
-                 "intermediate_size", "vocab_size"):  # fmt: skip
+    """The model configuration one of ``tp`` ranks sees: its share of heads, MLP channels and vocabulary.
+
+    With more ranks than KV heads (eight ranks, four KV heads) every KV head lives on ``tp / hkv`` consecutive
+    ranks: each of them projects, caches and reads that head's keys and values and owns a disjoint part of
+    the head's query heads, so the rank still sees whole GQA groups and nothing crosses ranks before ``o_proj``."""
+    for name in ("num_attention_heads", "linear_num_key_heads", "linear_num_value_heads", "intermediate_size", "vocab_size"):
         if getattr(cfg, name) % tp:
             raise ValueError(f"{name} = {getattr(cfg, name)} does not divide over {tp} ranks")
     if (cfg.intermediate_size // tp) % 128 or (cfg.linear_num_value_heads // tp * cfg.linear_value_head_dim) % 128:
@@ -52,7 +65,7 @@ def shard_config(cfg, tp: int):
     return dataclasses.replace(
         cfg,
         num_attention_heads=cfg.num_attention_heads // tp,
-        num_key_value_heads=cfg.num_key_value_heads // tp,
+        num_key_value_heads=kv_heads_per_rank(cfg, tp),
         linear_num_key_heads=cfg.linear_num_key_heads // tp,
         linear_num_value_heads=cfg.linear_num_value_heads // tp,
         intermediate_size=cfg.intermediate_size // tp,
@@ -76,12 +89,16 @@ def slice_columns(qw: QuantisedWeight, cols: Tensor | slice) -> QuantisedWeight:
 
 
 def slice_rows(qw: QuantisedWeight, k0: int, k1: int) -> QuantisedWeight:
-    """Rows ``[k0, k1)`` of the weight (whole scale groups), re-packed K-major: same nibbles, same scales."""
+    """Rows ``[k0, k1)`` of the weight (whole scale groups), re-packed K-major: same nibbles, same scales.
+
+    The shard keeps the parent's group size even where the reference's own packer would not pick it for a
+    matrix of that depth (``down_proj`` over eight ranks is 1152 rows = nine groups, an odd count, which
+    ``group_size_for`` refuses): a shard never goes through that packer, its groups are the parent's."""
     g = qw.group_size
     if k0 % g or k1 % g:
         raise ValueError(f"row slice [{k0}, {k1}) does not fall on {g}-row scale groups")
-    if group_size_for(k1 - k0) != g:
-        raise ValueError(f"a {k1 - k0}-row shard would not keep the group size {g}")
+    if (k1 - k0) % 2:
+        raise ValueError(f"a {k1 - k0}-row shard cannot be packed two rows to a byte")
     nib = unpack_k_major(qw.qweight)[k0:k1]
     return QuantisedWeight(pack_k_major(nib), qw.scale[k0 // g : k1 // g].contiguous(), qw.bits, g)
 
@@ -114,7 +131,7 @@ def shard_layer(lw: LayerWeights, cfg, rank: int, tp: int) -> LayerWeights:
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     qw = 2 * d if cfg.attn_output_gate else d
     q0, q1 = rank * hq // tp, (rank + 1) * hq // tp
-    g0, g1 = rank * hkv // tp, (rank + 1) * hkv // tp
+    g0, g1 = kv_head_range(cfg, rank, tp)  # with more ranks than KV heads: the one head all its query heads belong to
     cols = _cat([ar(q0 * qw, q1 * qw), ar(hq * qw + g0 * d, hq * qw + g1 * d), ar(hq * qw + hkv * d + g0 * d, hq * qw + hkv * d + g1 * d)], dev)
     return LayerWeights(
         kind=lw.kind, input_norm=lw.input_norm, post_norm=lw.post_norm,
@@ -131,6 +148,42 @@ def shard_weights(weights: ModelWeights, rank: int, tp: int) -> ModelWeights:
     out = ModelWeights(local, weights.embed, weights.final_norm, slice_columns(weights.head, slice(v0, v1)), weights.inv_freq)
     out.layers = [shard_layer(lw, cfg, rank, tp) for lw in weights.layers]
     return out
+
+
+def kv_head_range(cfg, rank: int, tp: int) -> tuple[int, int]:
+    """The KV heads ``[g0, g1)`` of the unsharded model that rank ``rank`` holds."""
+    hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    if hkv % tp == 0:
+        return rank * hkv // tp, (rank + 1) * hkv // tp
+    kv_heads_per_rank(cfg, tp)  # raises if the replicated layout does not apply
+    g0 = (rank * hq // tp) // (hq // hkv)
+    return g0, g0 + 1
+
+
+@torch.no_grad()
+def load_cache_shard(local_cache, whole_cache, cfg, rank: int, tp: int) -> None:
+    """Fill rank ``rank``'s cache (built for ``shard_config(cfg, tp)``) from an unsharded cache of ``cfg``: its KV
+    heads, its conv channels (the q, k and v blocks of its key / value heads) and its value heads' state."""
+    from .engine import cache_layer_tensors
+
+    hk, hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    g0, g1 = kv_head_range(cfg, rank, tp)
+    k0, k1, v0, v1 = rank * hk // tp, (rank + 1) * hk // tp, rank * hv // tp, (rank + 1) * hv // tp
+    kd = hk * dk
+    for wl, ll in zip(whole_cache.layers, local_cache.layers):
+        wt, lt = cache_layer_tensors(wl), cache_layer_tensors(ll)
+        if "keys" in wt:
+            n = min(lt["keys"].shape[2], wt["keys"].shape[2])
+            lt["keys"][:, :, :n].copy_(wt["keys"][:, g0:g1, :n])
+            lt["values"][:, :, :n].copy_(wt["values"][:, g0:g1, :n])
+        else:
+            dev = wt["conv"].device
+            rows = torch.cat([torch.arange(k0 * dk, k1 * dk), torch.arange(kd + k0 * dk, kd + k1 * dk),
+                              torch.arange(2 * kd + v0 * dv, 2 * kd + v1 * dv)]).to(dev)  # fmt: skip
+            lt["conv"].copy_(wt["conv"][:, rows])
+            lt["recurrent"].copy_(wt["recurrent"][:, v0:v1])
+    local_cache.seq_len = whole_cache.seq_len
 
 
 def weights_to(weights: ModelWeights, device) -> ModelWeights:
@@ -166,11 +219,14 @@ class TensorParallelEngine:
     ``group`` is a ``torch.distributed`` process group whose backend can reduce CUDA tensors (NCCL).
     """
 
-    def __init__(self, local_weights: ModelWeights, cache: DecodeCache, *, rank: int, tp: int, group=None, exchange: str = "nccl") -> None:
+    def __init__(self, local_weights: ModelWeights, cache: DecodeCache, *, rank: int, tp: int, group=None, exchange: str = "nccl",
+                 peer_slots: list[int] | None = None) -> None:  # fmt: skip
         """``exchange``: ``"nccl"`` adds the partial sums with ``torch.distributed.all_reduce`` between segments;
         ``"peer"`` gives every rank a symmetric exchange buffer (``torch.distributed._symmetric_memory``) and lets
         the kernels store into their peers' buffers and wait for one another: no collective call remains and the
-        whole token is one CUDA graph of this library's kernels. ``"peer"`` needs one GPU per rank."""
+        whole token is one CUDA graph of this library's kernels. ``"peer"`` needs one GPU per rank. ``peer_slots``:
+        for callers that map the ranks' exchange buffers themselves, the ``tp`` device pointers (entry ``rank`` is
+        this rank's own zeroed buffer of ``dfb_engine_tp_exchange_bytes``); without it symmetric memory is used."""
         import torch.distributed as dist
 
         if exchange not in ("nccl", "peer"):
@@ -180,7 +236,11 @@ class TensorParallelEngine:
         self.vocab_local = local_weights.config.vocab_size
         hidden = local_weights.config.hidden_size
         peer_ptrs = None
-        if exchange == "peer":
+        if exchange == "peer" and peer_slots is not None:
+            if len(peer_slots) != tp:
+                raise ValueError(f"peer_slots must hold {tp} device pointers, got {len(peer_slots)}")
+            peer_ptrs = [int(p) for p in peer_slots]
+        elif exchange == "peer":
             import torch.distributed._symmetric_memory as symm_mem
 
             lib = _lib.load()
@@ -206,6 +266,35 @@ class TensorParallelEngine:
         self.gathered = torch.zeros((tp, self.engine.batch, 2), dtype=torch.float32, device=dev)
         self._graph = None
         self._warm = False
+        self._lined_up = False
+        self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def _line_up(self) -> None:
+        """Peer exchange: the ranks' kernels wait on one another with a limit of about two seconds, so the hosts
+        must not start a step further apart than that. Everything slow and rank-local (graph capture) is done
+        first, then the ranks meet at a barrier; called at the start of every ``decode`` and of the first ``step``."""
+        eng = self.engine
+        if not eng._captured:
+            eng.capture()
+        torch.cuda.synchronize(eng.device)
+        self.dist.barrier(group=self.group)
+        self._lined_up = True
+
+    def check_status(self) -> None:
+        """Synchronise, combine the ranks' status words (maximum) and raise on every rank if any rank's kernels
+        gave up a wait: a rank that timed out has skipped a residual add, and what it stored for its peers
+        afterwards is wrong although their own status words stay zero."""
+        code = _lib.C.c_int(0)
+        _lib.check(self.lib.dfb_engine_status(self.engine._handle, _lib.C.byref(code), self.engine._stream()), "dfb_engine_status")
+        self._flag.fill_(code.value)
+        self.dist.all_reduce(self._flag, op=self.dist.ReduceOp.MAX, group=self.group)
+        worst = int(self._flag.item())
+        if worst:
+            raise _lib.Dfb200Error(
+                f"tensor-parallel step failed: a rank's kernels reported status {worst} (50: a peer's partial sums did not "
+                f"arrive within the wait limit; this rank's own status is {code.value}). Tokens, caches and recurrent state "
+                "after that point are not valid."
+            )
 
     def _run(self) -> None:
         stream = torch.cuda.current_stream(self.engine.device).cuda_stream
@@ -223,15 +312,21 @@ class TensorParallelEngine:
         masked = torch.where(vals == top, ids, torch.full_like(ids, float("inf")))
         self.engine.tokens.copy_(masked.min(dim=0).values.long())
 
-    def step(self, tokens: Tensor, *, graph: bool = False) -> Tensor:
+    def step(self, tokens: Tensor, *, graph: bool = False, check: bool = False) -> Tensor:
         """One token for every sequence; returns this rank's slice of the logits ``[batch, vocab / tp]``.
+        ``check`` (peer exchange): wait for the step and raise if any rank's kernels gave up a wait.
 
         By default the segments and the collectives between them are launched directly. With ``graph=True`` the
         first call still runs directly (that also sets NCCL's channels up) and from the second call on one CUDA
         graph per token, collectives included, is replayed."""
         eng = self.engine
         if self.exchange == "peer":  # the engine's own step: kernels only
-            return eng.step(tokens, graph=graph)
+            if not self._lined_up:
+                self._line_up()
+            out = eng.step(tokens, graph=True)
+            if check:
+                self.check_status()
+            return out
         self.cache.ensure_capacity(1)
         eng._sync_position()
         eng._set_tokens(tokens)
@@ -248,10 +343,16 @@ class TensorParallelEngine:
         eng._pos_host += 1
         return eng.logits
 
-    def decode(self, tokens: Tensor, steps: int, *, graph: bool = False) -> Tensor:
-        """Greedy loop on the device: returns the chosen tokens ``[batch, steps]`` (identical on every rank)."""
+    def decode(self, tokens: Tensor, steps: int, *, graph: bool = False, check: bool = True) -> Tensor:
+        """Greedy loop on the device: returns the chosen tokens ``[batch, steps]`` (identical on every rank).
+        With the peer exchange the ranks line up at a barrier first and, unless ``check`` is off, the call waits for
+        the tokens and raises on every rank if any rank's kernels gave up a wait."""
         if self.exchange == "peer":
-            return self.engine.decode(tokens, steps)
+            self._line_up()
+            out = self.engine.decode(tokens, steps)
+            if check:
+                self.check_status()
+            return out
         out = []
         t = tokens
         for _ in range(steps):

@@ -320,7 +320,11 @@ typedef struct dfb_model_desc {
    * waits (bounded, reporting through the status word) for all ranks' words, adds them in rank order and adds
    * the result to the residual stream; the token is picked across shards the same way. No collective library
    * call remains, dfb_engine_step / capture / replay / decode_host work as for one GPU, and every rank must
-   * run the same number of steps. One rank per GPU: kernels of different ranks wait on one another. */
+   * run the same number of steps. One rank per GPU: kernels of different ranks wait on one another. Every
+   * engine starts its epoch counter at 1, so the buffers must be zero when the engines are created (words left
+   * by an earlier engine would carry valid-looking tags), and a model may have at most 127 layers (254
+   * exchanges per token). A wait gives up after about two seconds and sets status 50; the ranks' hosts must
+   * therefore start a step within that time of one another (a barrier before the first launch). */
   void* const* tp_peer_slots;
 } dfb_model_desc;
 
@@ -365,8 +369,9 @@ int dfb_engine_trace_layer(void* engine, int layer);
 int dfb_engine_read_trace(void* engine, int64_t* out_host, int max_values, void* stream);
 /* How far ahead the kernels of a batch-1 step ask the L2 cache for weights: every launch requests, a slice
  * per CTA, the int4 words and scales of the projection `distance` GEMVs after the one it runs (or precedes),
- * so HBM keeps streaming while the kernels work through their dependent latencies. 0 switches it off; the
- * default is 1. Takes effect for steps enqueued or captured afterwards. No counterpart in the reference
+ * so HBM keeps streaming while the kernels work through their dependent latencies. 0 (the default) switches it
+ * off: under programmatic dependent launch the next kernel's own copies are normally in flight already, and on
+ * B200 the extra requests cost 1.5 to 3 % of the step. Takes effect for steps enqueued or captured afterwards. No counterpart in the reference
  * (its kernels rely on the hardware's own prefetching, src/deltaforge/kernels/tiled_gemv.py:452-454). */
 int dfb_engine_set_prefetch_distance(void* engine, int distance);
 /* Profiling of the graph-of-kernels step: with `buffer` (device memory, max_launches * ctas_per_launch * 8

@@ -35,28 +35,13 @@ def _rank_main(rank: int, world: int, port: int, results, two_devices: bool, exc
 
         cfg = ModelConfig(hidden_size=2560, intermediate_size=9216, num_hidden_layers=4, vocab_size=4096, layer_types=hybrid_layer_types(4))
         full = synth.random_model_weights(cfg, seed=3, device=dev, scale_dtype=torch.bfloat16)
-        ctx_len, steps = 200, 4
+        ctx_len, steps = 8192, 4  # the context the tensor-parallel benchmark configuration names
         # the whole model's cache, filled with seeded contents, and this rank's slice of it
-        whole_cache = E.DecodeCache(cfg, 1, 256, device=dev)
+        whole_cache = E.DecodeCache(cfg, 1, ctx_len + 64, device=dev)
         synth.fill_cache(whole_cache, ctx_len, seed=5)
         local_cfg = TP.shard_config(cfg, world)
-        cache = E.DecodeCache(local_cfg, 1, 256, device=dev)
-        hk, hv, hkv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.num_key_value_heads
-        dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
-        for wl, ll in zip(whole_cache.layers, cache.layers):
-            wt, lt = E.cache_layer_tensors(wl), E.cache_layer_tensors(ll)
-            if "keys" in wt:
-                g0, g1 = rank * hkv // world, (rank + 1) * hkv // world
-                lt["keys"].copy_(wt["keys"][:, g0:g1])
-                lt["values"].copy_(wt["values"][:, g0:g1])
-            else:
-                k0, k1, v0, v1 = rank * hk // world, (rank + 1) * hk // world, rank * hv // world, (rank + 1) * hv // world
-                kd = hk * dk
-                rows = torch.cat([torch.arange(k0 * dk, k1 * dk), torch.arange(kd + k0 * dk, kd + k1 * dk),
-                                  torch.arange(2 * kd + v0 * dv, 2 * kd + v1 * dv)]).to(dev)  # fmt: skip
-                lt["conv"].copy_(wt["conv"][:, rows])
-                lt["recurrent"].copy_(wt["recurrent"][:, v0:v1])
-        cache.seq_len = ctx_len
+        cache = E.DecodeCache(local_cfg, 1, ctx_len + 64, device=dev)
+        TP.load_cache_shard(cache, whole_cache, cfg, rank, world)
         eng = TP.TensorParallelEngine(TP.shard_weights(full, rank, world), cache, rank=rank, tp=world, exchange=exchange)
         tok = torch.tensor([17], device=dev)
         tp_logits, tp_tokens = [], []
@@ -125,9 +110,10 @@ def test_tensor_parallel_peer_exchange_matches_single_gpu():
 
 
 def test_peer_exchange_wait_runs_out_and_reports_status():
-    """A rank whose peer never shows up: the wait for the peer's partial sums is bounded (about 0.14 s per
-    kernel), the kernels return, the engine's status word says 50 and the CUDA context stays usable. The
-    'peer' here is a second local buffer that nothing fills, so no kernel waits for another kernel."""
+    """A rank whose peer never shows up: the wait for the peer's partial sums is bounded (about two seconds for
+    the first kernel that waits; once the status word is set every later wait gives up at once), the kernels
+    return, the engine's status word says 50 and the CUDA context stays usable. The 'peer' here is a second
+    local buffer that nothing fills, so no kernel waits for another kernel."""
     from deltaforge_b200 import _lib
     from deltaforge_b200 import engine as E
     from deltaforge_b200 import synth
@@ -147,3 +133,106 @@ def test_peer_exchange_wait_runs_out_and_reports_status():
         eng.check_status()
     assert int(absent.ne(0).sum()) > 0  # rank 0 did store its partial sums into the peer's buffer
     assert float(torch.ones(8, device=dev).sum()) == 8.0  # the context still works
+
+
+def test_tensor_parallel_decode_raises_when_a_peer_never_arrives():
+    """The same absent peer through ``TensorParallelEngine.decode``: the call must raise, not hand back tokens
+    computed from a residual stream that missed an add. One process stands in for the job (a one-rank gloo
+    group carries the barrier and the status reduction); rank 1's buffer is local memory nothing fills."""
+    import torch.distributed as dist
+
+    from deltaforge_b200 import _lib
+    from deltaforge_b200 import engine as E
+    from deltaforge_b200 import synth
+    from deltaforge_b200 import tp as TP
+    from deltaforge_b200.config import ModelConfig, hybrid_layer_types
+
+    dev = torch.device("cuda", 0)
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29917", rank=0, world_size=1)
+    try:
+        cfg = ModelConfig(hidden_size=2560, intermediate_size=9216, num_hidden_layers=4, vocab_size=4096, layer_types=hybrid_layer_types(4))
+        full = synth.random_model_weights(cfg, seed=3, device=dev, scale_dtype=torch.bfloat16)
+        cache = E.DecodeCache(TP.shard_config(cfg, 2), 1, 64, device=dev)
+        nbytes = _lib.load().dfb_engine_tp_exchange_bytes(1, cfg.hidden_size, 2)
+        mine = torch.zeros(nbytes // 8, dtype=torch.int64, device=dev)
+        absent = torch.zeros_like(mine)
+        eng = TP.TensorParallelEngine(TP.shard_weights(full, 0, 2), cache, rank=0, tp=2, exchange="peer",
+                                      peer_slots=[mine.data_ptr(), absent.data_ptr()])  # fmt: skip
+        with pytest.raises(_lib.Dfb200Error, match="status 50"):
+            eng.decode(torch.tensor([17], device=dev), 2)
+        assert int(eng.engine.tokens[0]) == -1  # the pick that could not complete left the mark, not a token
+        assert float(torch.ones(8, device=dev).sum()) == 8.0  # the context still works
+    finally:
+        if own_group:
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_sharded_step_emulated_on_one_gpu_matches_the_unsharded_engine(world):
+    """All ranks' shards on ONE GPU, driven segment by segment from the host, the fp32 partial sums added in
+    rank order between segments (what the all-reduce does): no kernel waits on another, so the eight-rank
+    sharding (each KV head on two ranks, nine-group ``down_proj`` shards, 31040... here 512 vocabulary columns per
+    rank) is checked against the unsharded engine wherever one GPU is all there is."""
+    import ctypes as C
+
+    from deltaforge_b200 import _lib
+    from deltaforge_b200 import engine as E
+    from deltaforge_b200 import synth
+    from deltaforge_b200 import tp as TP
+    from deltaforge_b200.config import ModelConfig, hybrid_layer_types
+
+    dev = torch.device("cuda", 0)
+    lib = _lib.load()
+    cfg = ModelConfig(hidden_size=2560, intermediate_size=9216, num_hidden_layers=4, vocab_size=4096, layer_types=hybrid_layer_types(4))
+    full = synth.random_model_weights(cfg, seed=3, device=dev, scale_dtype=torch.bfloat16)
+    ctx_len, steps = 1000, 3
+    whole_cache = E.DecodeCache(cfg, 1, ctx_len + 16, device=dev)
+    synth.fill_cache(whole_cache, ctx_len, seed=5)
+    local_cfg = TP.shard_config(cfg, world)
+    engines, partials = [], []
+    for r in range(world):
+        cache = E.DecodeCache(local_cfg, 1, ctx_len + 16, device=dev)
+        TP.load_cache_shard(cache, whole_cache, cfg, r, world)
+        eng = E.DecodeEngine(TP.shard_weights(full, r, world), cache, tp_size=world, tp_rank=r)
+        off = lib.dfb_engine_partial_buffer(eng._handle) - eng.workspace.data_ptr()
+        partials.append(eng.workspace[off : off + 4 * cfg.hidden_size].view(torch.float32))
+        engines.append(eng)
+    ref = E.DecodeEngine(full, whole_cache)
+    segments = lib.dfb_engine_num_segments(engines[0]._handle)
+    assert segments == 2 * cfg.num_hidden_layers + 1
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    tok = torch.tensor([17], device=dev)
+    for _ in range(steps):
+        for eng in engines:
+            eng.cache.ensure_capacity(1)
+            eng._sync_position()
+            eng._set_tokens(tok)
+        for seg in range(segments):
+            for eng in engines:
+                _lib.check(lib.dfb_engine_step_segment(eng._handle, seg, C.c_void_p(stream)), "dfb_engine_step_segment")
+            if seg + 1 < segments:
+                total = partials[0].clone()
+                for p in partials[1:]:
+                    total += p  # rank order, fp32
+                for p in partials:
+                    p.copy_(total)
+        for eng in engines:
+            eng.cache.advance(1)
+            eng._pos_host += 1
+        logits = torch.cat([eng.logits for eng in engines], dim=-1)
+        want = ref.step(tok).clone()
+        scale = want.float().std().item()
+        err = (want.float() - logits.float()).abs().max().item()
+        assert err < 6e-2 * scale, f"max logit error {err:.4g} at scale {scale:.4g}"
+        if want.float().topk(2).values.diff().abs().item() > 2 * err:
+            assert int(logits.float().argmax(-1)) == int(want.argmax(-1))
+        tok = want.argmax(-1).reshape(1)
+    for eng in engines + [ref]:
+        eng.check_status()
+    # the KV rows written during the steps: a head that lives on two ranks holds the same rows on both
+    if world == 8:
+        a = E.cache_layer_tensors(engines[0].cache.layers[3])["keys"]
+        b = E.cache_layer_tensors(engines[1].cache.layers[3])["keys"]
+        assert torch.equal(a, b)
