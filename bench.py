@@ -294,7 +294,8 @@ def run_ours(args) -> dict | None:
     cache = E.DecodeCache(cfg, BATCH, CONTEXT + steps + warmup + 8, device=dev)
     synth.fill_cache(cache, CONTEXT, seed=77 + rank)
     snap = cache.snapshot()
-    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent", prefetch_distance=args.prefetch_distance)
+    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent", prefetch_distance=args.prefetch_distance,
+                         tensor_core_gemv=not args.no_tensor_core_gemv)
     tok = torch.full((BATCH,), 1000 + rank, dtype=torch.int64, device=dev)
     eng.capture()
 
@@ -600,6 +601,7 @@ def main() -> None:
     ap.add_argument("--tp", action="store_true", help="all ranks form one tensor-parallel replica (not the default data-parallel run)")
     ap.add_argument("--tp-exchange", choices=("nccl", "peer"), default="nccl", help="with --tp: how the ranks add their partial sums")
     ap.add_argument("--tp-graph", action="store_true", help="with --tp: record kernels and collectives into one CUDA graph per token")
+    ap.add_argument("--no-tensor-core-gemv", action="store_true", help="run the layer projections on the dp4a kernels instead of the integer mma")
     ap.add_argument("--timeline", default=None, help="after the timed runs, write a per-launch timeline of one step to this file")
     ap.add_argument("--prefetch-distance", type=int, default=None,
                     help="projections ahead for which the step's kernels ask the L2 for weights (0: off; default: the library's)")

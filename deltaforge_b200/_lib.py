@@ -23,7 +23,7 @@ class GemvDesc(C.Structure):
         ("epilogue", c_i32), ("out", c_vp), ("out_stride", c_i64), ("residual", c_vp), ("residual_stride", c_i64),
         ("conv_state", c_vp), ("conv_w", c_vp), ("conv_dim", c_i32),
         ("scratch", c_vp), ("scratch_bytes", c_sz), ("math", c_i32), ("force_tiled", c_i32),
-        ("packed_k8", c_vp),
+        ("packed_k8", c_vp), ("packed_mma", c_vp),
     ]  # fmt: skip
 
 
@@ -71,7 +71,7 @@ class AttnStepDesc(C.Structure):
 class Linear(C.Structure):
     _fields_ = [
         ("packed", c_vp), ("scale", c_vp), ("scale_is_bf16", c_i32), ("K", c_i32), ("N", c_i32), ("group", c_i32),
-        ("packed_k8", c_vp),
+        ("packed_k8", c_vp), ("packed_mma", c_vp), ("mma_pair", c_i32),
     ]  # fmt: skip
 
 
@@ -102,9 +102,13 @@ class ModelDesc(C.Structure):
 SIGNATURES = {
     "dfb_last_error": (C.c_char_p, []),
     "dfb_abi_version": (C.c_int, []),
+    "dfb_int4_group_size": (C.c_int, [C.c_int]),
+    "dfb_int4_quantise_k_major": (C.c_int, [c_vp, C.c_int, C.c_int, C.c_int, c_vp, c_vp, c_vp]),
     "dfb_int4_unpack": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_dequant": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_repack_k8": (C.c_int, [c_vp, C.c_int, C.c_int, c_vp, c_vp]),
+    "dfb_int4_repack_mma_bytes": (c_sz, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "dfb_int4_repack_mma": (C.c_int, [c_vp, c_vp, C.c_int, C.c_int, C.c_int, C.c_int, c_vp, c_vp]),
     "dfb_int4_gemv_scratch_bytes": (c_sz, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "dfb_int4_gemv": (C.c_int, [C.POINTER(GemvDesc), c_vp]),
     "dfb_int4_gemv_static_max_partials_bytes": (c_sz, []),

@@ -50,6 +50,20 @@ extern "C" {
 const char* dfb_last_error(void) { return g_error; }
 int dfb_abi_version(void) { return 1; }
 
+int dfb_int4_group_size(int K) {
+  if (K <= 0 || K % 2) return 0;
+  const int group = K % 256 == 0 ? 128 : K / 2;
+  return (group & (group - 1)) ? 0 : group;
+}
+
+int dfb_int4_quantise_k_major(const void* weight, int weight_is_bf16, int N, int K, uint8_t* packed, float* scale, void* stream) {
+  if (!weight || !packed || !scale) return bad("dfb_int4_quantise_k_major: null pointer");
+  if (N <= 0 || K <= 0) return bad("dfb_int4_quantise_k_major: bad shape N=%d K=%d", N, K);
+  const int group = dfb_int4_group_size(K);
+  if (group == 0) return bad("dfb_int4_quantise_k_major: K=%d is odd, or half of it is not a power of two where K is not a multiple of 256", K);
+  return launch_int4_quantise(weight, weight_is_bf16, N, K, group, packed, scale, (cudaStream_t)stream);
+}
+
 int dfb_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, void* stream) {
   if (!packed || !out) return bad("dfb_int4_unpack: null pointer");
   if (K <= 0 || K % 2 || N <= 0) return bad("dfb_int4_unpack: bad shape K=%d N=%d", K, N);
@@ -67,6 +81,18 @@ int dfb_int4_repack_k8(const uint8_t* packed, int K, int N, void* out, void* str
   if (!packed || !out) return bad("dfb_int4_repack_k8: null pointer");
   if (K <= 0 || K % 8 || N <= 0) return bad("dfb_int4_repack_k8: K must be a positive multiple of 8, got K=%d N=%d", K, N);
   return launch_int4_repack_k8(packed, K, N, (uint32_t*)out, (cudaStream_t)stream);
+}
+
+size_t dfb_int4_repack_mma_bytes(int K, int N, int pair, int scale_is_bf16) {
+  if (K <= 0 || K % 128 || N <= 0 || (pair && N % 2)) return 0;
+  return mma_repack_bytes(K, N, pair, scale_is_bf16);
+}
+
+int dfb_int4_repack_mma(const uint8_t* packed, const void* scale, int scale_is_bf16, int K, int N, int pair, void* out, void* stream) {
+  if (!packed || !scale || !out) return bad("dfb_int4_repack_mma: null pointer");
+  if (K <= 0 || K % 128 || N <= 0 || (pair && N % 2))
+    return bad("dfb_int4_repack_mma: K must be a positive multiple of 128 and N positive (even for a gate|up pair), got K=%d N=%d", K, N);
+  return launch_int4_repack_mma(packed, scale, scale_is_bf16, K, N, pair, out, (cudaStream_t)stream);
 }
 
 size_t dfb_int4_gemv_scratch_bytes(int rows, int K, int N, int group) {
@@ -116,6 +142,7 @@ int dfb_int4_gemv(const dfb_gemv_desc* d, void* stream) {
   p.conv_w = (const bf16*)d->conv_w;
   p.conv_dim = d->conv_dim;
   p.math = d->math;
+  p.packed_mma = (const unsigned char*)d->packed_mma;
   if (need) {
     p.partials = (float*)d->scratch;
     p.counters = (unsigned*)((char*)d->scratch + align_up(gemv_partials_bytes(d->rows, d->K, d->N, d->group), 256));

@@ -197,6 +197,11 @@ struct Engine {
     p.rows = m.batch;
     p.packed = l.packed;
     p.packed_k8 = (const uint32_t*)l.packed_k8;
+    // the gate|up pair layout serves the SwiGLU epilogue only; every other copy serves every other epilogue
+    if (l.packed_mma && (l.mma_pair != 0) == (epilogue == EPI_SWIGLU)) {
+      p.packed_mma = (const unsigned char*)l.packed_mma;
+      p.mma_pair = l.mma_pair;
+    }
     p.scale = l.scale;
     p.scale_bf16 = l.scale_is_bf16;
     p.K = l.K;
@@ -233,7 +238,7 @@ struct Engine {
       p.ss_count = h_tiles;
     }
     if (epilogue == EPI_RESIDUAL) {
-      ss_valid = m.batch == 1 && h_tiles <= 256 && l.N < 65536 && cluster_path_ok(p);
+      ss_valid = m.batch == 1 && h_tiles <= 256 && l.N < 65536 && (mma_path_ok(p) || cluster_path_ok(p));
       if (ss_valid) p.ss_out = (float*)at(ws.h_ss);
     }
     ++launches;
@@ -279,13 +284,15 @@ struct Engine {
     return c;
   }
   bool attn_defer_merge(const dfb_layer_desc& L) const {
-    if (m.batch != 1 || tp() || m.math != MATH_FAST || !L.out_proj.packed_k8) return false;
+    if (m.batch != 1 || tp() || m.math != MATH_FAST || !(L.out_proj.packed_k8 || L.out_proj.packed_mma)) return false;
     if (!attn_step_ok(m.head_dim, m.hq, m.hkv, m.rotary_dim, m.attn_splits, m.max_seq)) return false;
     const int ncl = m.attn_splits / attn_cluster_size();
-    if (ncl < 2 || ncl > 16) return false;
+    if (ncl < 2 || ncl > 8) return false;
     GemvParams q = {};
     q.rows = 1;
     q.packed_k8 = (const uint32_t*)L.out_proj.packed_k8;
+    if (L.out_proj.packed_mma && !L.out_proj.mma_pair) q.packed_mma = (const unsigned char*)L.out_proj.packed_mma;
+    q.scale_bf16 = L.out_proj.scale_is_bf16;
     q.scale = L.out_proj.scale;
     q.K = L.out_proj.K, q.N = L.out_proj.N, q.group = L.out_proj.group;
     q.prologue = PRO_ATTN_MERGE;
@@ -296,7 +303,7 @@ struct Engine {
     q.merge.ml = q.merge.acc;
     q.merge.nclusters = ncl;
     q.merge.d = m.head_dim;
-    return cluster_path_ok(q);
+    return mma_path_ok(q) || (q.packed_k8 && cluster_path_ok(q));
   }
 
   int mixer_attention(const dfb_layer_desc& L, bf16* proj, long pstride, bf16* mix, bf16* qout, cudaStream_t s) {
@@ -460,10 +467,15 @@ struct Engine {
   }
 
   bool swiglu_in_gate_up(const dfb_layer_desc& L) const {
-    if (m.batch != 1 || tp() || m.math != MATH_FAST || !L.gate_up.packed_k8) return false;
+    if (m.batch != 1 || tp() || m.math != MATH_FAST || !(L.gate_up.packed_k8 || L.gate_up.packed_mma)) return false;
     GemvParams q = {};
     q.rows = 1;
     q.packed_k8 = (const uint32_t*)L.gate_up.packed_k8;
+    if (L.gate_up.packed_mma && L.gate_up.mma_pair) {
+      q.packed_mma = (const unsigned char*)L.gate_up.packed_mma;
+      q.mma_pair = 1;
+    }
+    q.scale_bf16 = L.gate_up.scale_is_bf16;
     q.scale = L.gate_up.scale;
     q.K = L.gate_up.K, q.N = L.gate_up.N, q.group = L.gate_up.group;
     q.prologue = PRO_RMSNORM;
@@ -471,7 +483,7 @@ struct Engine {
     q.math = MATH_FAST;
     q.x = (const bf16*)at(ws.h);
     q.norm_w = (const bf16*)L.post_norm_w;
-    return cluster_path_ok(q);
+    return mma_path_ok(q) || (q.packed_k8 && cluster_path_ok(q));
   }
 
   int second_half(int i, cudaStream_t s) {  // SwiGLU MLP

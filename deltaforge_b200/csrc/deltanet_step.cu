@@ -144,9 +144,11 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
     if (j < dk) (is_k ? kn : qn)[j] = xn;
   }
   __syncthreads();
+  if (t == 0) trace_mark(p.trace, cta, 2);
 
   // 3. Recurrence; the updated slab goes straight back.
   const float o = delta_core(s, dk, col_ok, qn, kn, vval, gates[1], gates[0], red);
+  if (t == 0) trace_mark(p.trace, cta, 3);
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int k = warp * RPT + i;
@@ -163,6 +165,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   }
   const float sz = silu_f(zval);  // needs nothing from the other CTAs: evaluated while their sums arrive
   cluster.sync();
+  if (t == 0) trace_mark(p.trace, cta, 5);
   float tot = 0.f;
   for (int rk = 0; rk < nvb; ++rk) tot += cluster_ss[rk];
   if (warp == 0 && col_ok) {

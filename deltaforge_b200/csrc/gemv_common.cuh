@@ -51,26 +51,39 @@ __device__ __forceinline__ float prologue_apply(int prologue, float xv, float wv
   return xv;
 }
 
-// PRO_ATTN_MERGE: the four activation values k .. k+3 (k a multiple of 4) of the gated attention output.
+// PRO_ATTN_MERGE: the four activation values k .. k+3 (k a multiple of 4) of the gated attention output. All loads
+// (every cluster's (m, l) pair and its four partial sums) are issued before anything is computed: one round trip.
 __device__ __forceinline__ void attn_merge_values(const AttnMerge& a, int k, float (&v)[4]) {
+  constexpr int MAXC = 8;  // cluster_path_ok() admits at most this many
   const int h = k / a.d, i = k % a.d;
-  const float* ml = a.ml + (long)h * a.nclusters * 2;
-  float mg = -INFINITY;
-  for (int c = 0; c < a.nclusters; ++c) mg = fmaxf(mg, __ldcg(ml + 2 * c));
-  float o[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
-  for (int c = 0; c < a.nclusters; ++c) {  // fixed order: the same bits every run
-    const float m = __ldcg(ml + 2 * c);
-    const float w = (m == -INFINITY) ? 0.f : __expf(m - mg);
-    l = fmaf(w, __ldcg(ml + 2 * c + 1), l);
-    const float4 pa = __ldcg((const float4*)(a.acc + ((long)h * a.nclusters + c) * a.d + i));
-    o[0] = fmaf(w, pa.x, o[0]), o[1] = fmaf(w, pa.y, o[1]), o[2] = fmaf(w, pa.z, o[2]), o[3] = fmaf(w, pa.w, o[3]);
+  const float2* ml = (const float2*)(a.ml + (long)h * a.nclusters * 2);
+  const float* acc = a.acc + (long)h * a.nclusters * a.d + i;
+  float2 mlv[MAXC];
+  float4 pa[MAXC];
+  uint2 graw = make_uint2(0u, 0u);
+  if (a.gate) graw = *(const uint2*)(a.gate + (long)h * a.gateh_stride + i);
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    mlv[c] = c < a.nclusters ? __ldcg(ml + c) : make_float2(-INFINITY, 0.f);
+    pa[c] = c < a.nclusters ? __ldcg((const float4*)(acc + (long)c * a.d)) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  float mg = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) mg = fmaxf(mg, mlv[c].x);
+  float o[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {  // fixed order: the same bits every run
+    const float w = (mlv[c].x == -INFINITY) ? 0.f : __expf(mlv[c].x - mg);
+    l = fmaf(w, mlv[c].y, l);
+    o[0] = fmaf(w, pa[c].x, o[0]), o[1] = fmaf(w, pa[c].y, o[1]), o[2] = fmaf(w, pa[c].z, o[2]), o[3] = fmaf(w, pa[c].w, o[3]);
+  }
+  const float gl[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xffff0000u), __uint_as_float(graw.y << 16),
+                       __uint_as_float(graw.y & 0xffff0000u)};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float y = round_bf16(o[j] / l);
     if (a.gate) {
-      const float gv = bf2f(a.gate[(long)h * a.gateh_stride + i + j]);
-      const float gg = round_bf16(a.gate_swish ? silu_f(gv) : sigmoid_f(gv));
+      const float gg = round_bf16(a.gate_swish ? silu_f(gl[j]) : sigmoid_f(gl[j]));
       y = round_bf16(__fmul_rn(y, gg));
     }
     v[j] = y;

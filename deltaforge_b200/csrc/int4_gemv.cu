@@ -388,6 +388,7 @@ static int configure_rows() {
 int gemv_configure() {
   if (int rc = stream_configure()) return rc;
   if (int rc = cluster_configure()) return rc;
+  if (int rc = mma_configure()) return rc;
   if (int rc = tc_configure()) return rc;
   if (int rc = configure_rows<1>()) return rc;
   if (int rc = configure_rows<2>()) return rc;
@@ -415,6 +416,7 @@ int launch_gemv(const GemvParams& p, cudaStream_t stream) {
   static OncePerDevice once;
   const int configured = once.run(gemv_configure);
   if (configured) return configured;
+  if (!p.force_tiled && p.status && p.rows == 1 && mma_path_ok(p)) return launch_gemv_mma(p, p.status, stream);
   if ((p.epilogue == EPI_SWIGLU || p.prologue == PRO_ATTN_MERGE) && !(!p.force_tiled && p.status && p.N < 65536 && cluster_path_ok(p))) {
     set_error("int4 gemv: the SwiGLU epilogue and the attention-merge prologue exist in the cluster kernel only (one row, "
               "re-packed group-128 weight; SwiGLU: N a multiple of two tiles)");

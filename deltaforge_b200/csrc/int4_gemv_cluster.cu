@@ -131,7 +131,7 @@ struct ClusterArgs {
 constexpr int MAX_TPC = 4;
 
 // TNW: columns per tile. CW: consumer warps (8 or 16); one more warp issues the copies.
-template <int TNW, int CW>
+template <int TNW, int CW, bool NS>  // NS: odd rows' nibbles are used unshifted (16 x their value) in accumulators of their own
 __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid_constant__ CUtensorMap wmap,
                                                                     const __grid_constant__ CUtensorMap smap, const ClusterArgs a) {
   constexpr int CT = CW * 32;          // consumer threads
@@ -158,12 +158,11 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
   const int cs = a.cs;
   const int rank = (int)cluster_rank();
   const int cluster = blockIdx.x / cs;
-  // A cluster's tiles are neighbours, except under the SwiGLU epilogue, where they are a tile of gate_proj columns
-  // and the tile of up_proj columns of the same channels (half the matrix further on).
+  // Under the SwiGLU epilogue (TNW = 256) a tile is 128 gate_proj columns and the 128 up_proj columns of the same
+  // channels, half the matrix further on: two boxes of 128 columns per unit, each laid out [16 rows][128 columns].
   const bool swiglu = p.epilogue == EPI_SWIGLU;
-  const int tile_step = swiglu ? a.num_tiles / 2 : 1;
-  const int tile0 = swiglu ? cluster : cluster * a.tpc;
-  const int ntiles = swiglu ? 2 : min(a.tpc, a.num_tiles - tile0);  // >= 1: the grid holds no empty cluster
+  const int tile0 = cluster * a.tpc;
+  const int ntiles = min(a.tpc, a.num_tiles - tile0);  // >= 1: the grid holds no empty cluster
   const int g0 = (int)((long)rank * G / cs), g1 = (int)((long)(rank + 1) * G / cs);
   const int nunits = g1 - g0;
   const int total = ntiles * nunits;
@@ -196,8 +195,16 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
         }
         unsigned char* dst = ring + (size_t)st * STAGE;
         mbar_expect_tx(&full[st], W_BYTES + scale_bytes);
-        tma_load_2d(dst, &wmap, (tile0 + i * tile_step) * TNW, (g0 + s) * UROWS, &full[st], pol);
-        tma_load_2d(dst + W_BYTES, &smap, (tile0 + i * tile_step) * TNW, g0 + s, &full[st], pol);
+        if (swiglu) {
+          const int cg = (tile0 + i) * (TNW / 2), cu = p.N / 2 + cg;
+          tma_load_2d(dst, &wmap, cg, (g0 + s) * UROWS, &full[st], pol);
+          tma_load_2d(dst + W_BYTES / 2, &wmap, cu, (g0 + s) * UROWS, &full[st], pol);
+          tma_load_2d(dst + W_BYTES, &smap, cg, g0 + s, &full[st], pol);
+          tma_load_2d(dst + W_BYTES + scale_bytes / 2, &smap, cu, g0 + s, &full[st], pol);
+        } else {
+          tma_load_2d(dst, &wmap, (tile0 + i) * TNW, (g0 + s) * UROWS, &full[st], pol);
+          tma_load_2d(dst + W_BYTES, &smap, (tile0 + i) * TNW, g0 + s, &full[st], pol);
+        }
         if (++s == nunits) s = 0, ++i;
         if (++st == a.stages) st = 0, ++round;
         if (j + 1 == min(total, a.stages)) {
@@ -223,7 +230,7 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
       if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
       if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
     }
-    if ((cs == 1 || rank == 0) && t < TNW && tile0 * TNW + t < p.N) pre = epilogue_preload(p, 0, tile0 * TNW + t);
+    if ((cs == 1 || rank == 0) && !swiglu && t < TNW && tile0 * TNW + t < p.N) pre = epilogue_preload(p, 0, tile0 * TNW + t);
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
       float tot = 0.f;
@@ -288,6 +295,10 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
     if (t == 0) trace_mark(p.trace, cta, 2);
 
     const int rl = t / CQ, cq = t % CQ;
+    // where this thread's four columns sit inside a stage: one [16][TNW] block, or (SwiGLU) two [16][TNW/2] blocks
+    const int w_row = swiglu ? TNW * 2 : TNW * 4;
+    const int w_off = swiglu ? (cq / (CQ / 2)) * (W_BYTES / 2) + (cq % (CQ / 2)) * 16 : cq * 16;
+    const int s_quad = swiglu ? (cq / (CQ / 2)) * (CQ / 2) + (cq % (CQ / 2)) : cq;  // scale rows are [gate half | up half] too
     int st = 0, phase = 0;
     for (int i = 0; i < ntiles; ++i) {
       float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -303,32 +314,42 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
           for (int r = 0; r < RPT; ++r) {
             const int kb = rl + RL * r;
             const uint4 xw = *(const uint4*)(xq + (s * UROWS + kb) * 16);
-            const uint4 w4 = *(const uint4*)(wbase + kb * (TNW * 4) + cq * 16);
+            const uint4 w4 = *(const uint4*)(wbase + kb * w_row + w_off);
             msum += mk[s * UROWS + kb];
             const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const uint32_t ne = wv[q] & 0x0F0F0F0Fu, no = wv[q] & 0xF0F0F0F0u;
-              acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
-              acc_oh[q] = dp4a_us(no, xw.y, acc_oh[q]);
-              acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
-              acc_ol[q] = dp4a_uu(no, xw.w, acc_ol[q]);
+              const uint32_t ne = wv[q] & 0x0F0F0F0Fu;
+              if (NS) {
+                const uint32_t no = wv[q] & 0xF0F0F0F0u;
+                acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
+                acc_oh[q] = dp4a_us(no, xw.y, acc_oh[q]);
+                acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
+                acc_ol[q] = dp4a_uu(no, xw.w, acc_ol[q]);
+              } else {
+                const uint32_t no = (wv[q] >> 4) & 0x0F0F0F0Fu;
+                acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
+                acc_eh[q] = dp4a_us(no, xw.y, acc_eh[q]);
+                acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
+                acc_el[q] = dp4a_uu(no, xw.w, acc_el[q]);
+              }
             }
           }
           float sc[4];
           if (p.scale_bf16) {
-            const uint2 v = *(const uint2*)(wbase + W_BYTES + cq * 8);
+            const uint2 v = *(const uint2*)(wbase + W_BYTES + s_quad * 8);
             sc[0] = __uint_as_float(v.x << 16), sc[1] = __uint_as_float(v.x & 0xffff0000u);
             sc[2] = __uint_as_float(v.y << 16), sc[3] = __uint_as_float(v.y & 0xffff0000u);
           } else {
-            const float4 v = *(const float4*)(wbase + W_BYTES + cq * 16);
+            const float4 v = *(const float4*)(wbase + W_BYTES + s_quad * 16);
             sc[0] = v.x, sc[1] = v.y, sc[2] = v.z, sc[3] = v.w;
           }
           const float f = fg[s];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             // sum over this thread's rows of (nibble - 8) * m, exact: the odd-row part is a multiple of 16
-            const int S = (acc_eh[q] * 256 + acc_el[q]) + ((acc_oh[q] * 256 + acc_ol[q]) >> 4) - 8 * msum;
+            const int S = NS ? (acc_eh[q] * 256 + acc_el[q]) + ((acc_oh[q] * 256 + acc_ol[q]) >> 4) - 8 * msum
+                             : acc_eh[q] * 256 + acc_el[q] - 8 * msum;
             tot[q] = fmaf((float)S * f, sc[q], tot[q]);
           }
           if (a.stages < total) {  // the stage goes back to the producer (only when units outnumber stages)
@@ -366,16 +387,22 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
   else __syncthreads();
   if (t == 0) trace_mark(p.trace, cta, 5);
   if (swiglu) {
-    // rank 0 holds the gate_proj and the up_proj sums of the same TNW channels: bf16(silu(g)) * u, rounded as the
-    // reference's SwiGLUMLP rounds it (src/deltaforge/reference.py:692-693, src/deltaforge/kernels/fused_swiglu.py:18-22)
-    if (rank == 0 && t < TNW && tile0 * TNW + t < p.N / 2) {
-      float g = 0.f, u = 0.f;
-      for (int r = 0; r < cs; ++r) {
-        g += dsm[r * TNW + t];
-        u += dsm[(cs + r) * TNW + t];
+    // rank 0 holds, per tile, the gate_proj sums of TNW/2 channels (threads 0 .. TNW/2-1) and their up_proj sums (the
+    // other half): bf16(silu(g)) * u, rounded as the reference's SwiGLUMLP rounds it (src/deltaforge/reference.py:692-693,
+    // src/deltaforge/kernels/fused_swiglu.py:18-22)
+    if (rank == 0 && t < TNW) {
+      for (int i = 0; i < ntiles; ++i) {
+        float v = 0.f;
+        for (int r = 0; r < cs; ++r) v += dsm[(i * cs + r) * TNW + t];
+        red[t] = v;
+        asm volatile("bar.sync 2, %0;" ::"n"(TNW) : "memory");
+        const int ch = (tile0 + i) * (TNW / 2) + t;
+        if (t < TNW / 2 && ch < p.N / 2) {
+          const float sv = round_bf16(silu_f(round_bf16(red[t])));
+          p.out[ch] = f2bf(__fmul_rn(sv, round_bf16(red[t + TNW / 2])));
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(TNW) : "memory");
       }
-      const float sv = round_bf16(silu_f(round_bf16(g)));
-      p.out[tile0 * TNW + t] = f2bf(__fmul_rn(sv, round_bf16(u)));
     }
   } else if (rank == 0 && t < TNW) {
     for (int i = 0; i < ntiles; ++i) {
@@ -431,24 +458,30 @@ ClusterPlan plan_cluster(int K, int N, bool swiglu) {
   ClusterPlan c = {};
   const int G = K / 128;
   c.cs = pick_cs(K);
-  c.max_units = (G + c.cs - 1) / c.cs;
   c.tiles = (N + TNW - 1) / TNW;
-  c.cw = env_int("DFB_CW", 16);
+  if (swiglu) {
+    // a tile pairs TNW/2 gate columns with their up columns; small clusters place well (the CTAs of a cluster must sit
+    // in one GPC, and GPCs of 18 or 20 SMs hold only 34 clusters of four single-CTA-per-SM blocks but 74 of two)
+    c.cs = std::min(c.cs, env_int("DFB_SWIGLU_CS", 2));
+    c.tiles = (N / 2 + TNW / 2 - 1) / (TNW / 2);
+  }
+  c.max_units = (G + c.cs - 1) / c.cs;
+  c.cw = env_int("DFB_CW", 8);
   const int sms = 148;
   const int ctas = c.tiles * c.cs;
   c.tpc = ctas > env_int("DFB_FOLD_ABOVE", 222) ? std::min(MAX_TPC, (ctas + sms - 1) / sms) : 1;
-  if (swiglu) c.tpc = 2;  // a gate tile and its up tile per cluster
   c.clusters = (c.tiles + c.tpc - 1) / c.tpc;
   const size_t stage = (size_t)UROWS * TNW * 4 + TNW * 4;
-  c.stages = c.max_units;
-  if (c.tpc > 1) c.stages = std::min(c.tpc * c.max_units, std::max(c.max_units, (int)(((size_t)env_int("DFB_RING_KB", 108) << 10) / stage)));
+  // everything resident when it fits in about 100 KB (two CTAs per SM); a ring of stages the consumers recycle otherwise
+  const int ring_cap = (int)(((size_t)env_int("DFB_RING_KB", 125) << 10) / stage);
+  c.stages = std::min(c.tpc * c.max_units, std::max(env_int("DFB_MIN_STAGES", 5), ring_cap));
   const int rl = c.cw * 32 / (TNW / 4);
   c.smem = (size_t)c.stages * stage + (size_t)c.max_units * UROWS * 16 + (size_t)c.max_units * UROWS * 4 +
            (size_t)((c.max_units + 3) & ~3) * 4 + (size_t)rl * TNW * 4 + (size_t)c.tpc * c.cs * TNW * 4 + (size_t)c.stages * 16 + 64 + 128;
   return c;
 }
 
-template <int TNW, int CW>
+template <int TNW, int CW, bool NS>
 int launch_cluster_cfg(const GemvParams& p, const ClusterPlan& c, const CUtensorMap& wmap, const CUtensorMap& smap, int* status,
                        cudaStream_t stream) {
   ClusterArgs a = {};
@@ -473,7 +506,7 @@ int launch_cluster_cfg(const GemvParams& p, const ClusterPlan& c, const CUtensor
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW, CW>, wmap, smap, a);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW, CW, NS>, wmap, smap, a);
   if (e != cudaSuccess) {
     set_error("int4 gemv (cluster): launch failed: %s", cudaGetErrorString(e));
     return 1;
@@ -492,7 +525,7 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
   {
     const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)(p.K / 8)};
     const cuuint64_t strides[1] = {(cuuint64_t)p.N * 4};
-    const cuuint32_t box[2] = {TNW, UROWS};
+    const cuuint32_t box[2] = {(cuuint32_t)(p.epilogue == EPI_SWIGLU ? TNW / 2 : TNW), UROWS};
     const cuuint32_t es[2] = {1, 1};
     const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)p.packed_k8, dims, strides, box, es,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -506,7 +539,7 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
     const int esz = p.scale_bf16 ? 2 : 4;
     const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)(p.K / 128)};
     const cuuint64_t strides[1] = {(cuuint64_t)p.N * esz};
-    const cuuint32_t box[2] = {TNW, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)(p.epilogue == EPI_SWIGLU ? TNW / 2 : TNW), 1};
     const cuuint32_t es[2] = {1, 1};
     const CUresult r = enc(&smap, p.scale_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                            (void*)p.scale, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -517,8 +550,9 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
     }
   }
   const ClusterPlan c = plan_cluster<TNW>(p.K, p.N, p.epilogue == EPI_SWIGLU);
-  if (c.cw == 8) return launch_cluster_cfg<TNW, 8>(p, c, wmap, smap, status, stream);
-  return launch_cluster_cfg<TNW, 16>(p, c, wmap, smap, status, stream);
+  if (c.cw == 8 && env_int("DFB_NOSHIFT", 0)) return launch_cluster_cfg<TNW, 8, true>(p, c, wmap, smap, status, stream);
+  if (c.cw == 8) return launch_cluster_cfg<TNW, 8, false>(p, c, wmap, smap, status, stream);
+  return launch_cluster_cfg<TNW, 16, true>(p, c, wmap, smap, status, stream);
 }
 
 }  // namespace
@@ -530,15 +564,15 @@ bool cluster_path_ok(const GemvParams& p) {
         ((uintptr_t)p.packed_k8 % 16) == 0 && ((uintptr_t)p.scale % 16) == 0 && p.math == MATH_FAST &&
         ((uintptr_t)p.x % 8) == 0 && (p.prologue != PRO_RMSNORM || ((uintptr_t)p.norm_w % 8) == 0) &&
         (p.prologue != PRO_SILU_MUL || ((uintptr_t)p.up % 8) == 0) &&
-        (p.prologue != PRO_ATTN_MERGE || (p.merge.acc && p.merge.ml && p.merge.nclusters >= 1 && p.merge.nclusters <= 16 &&
+        (p.prologue != PRO_ATTN_MERGE || (p.merge.acc && p.merge.ml && p.merge.nclusters >= 1 && p.merge.nclusters <= 8 &&
                                           p.merge.d % 128 == 0 && p.K % p.merge.d == 0 && ((uintptr_t)p.merge.acc % 16) == 0))))
     return false;
   const bool swiglu = p.epilogue == EPI_SWIGLU;
   const int tnw = cluster_tile_width(p.N);
-  if (swiglu && (p.N % (2 * tnw) != 0)) return false;  // whole tiles of gate columns, then whole tiles of up columns
+  if (swiglu && (tnw != 256 || p.N % 8 != 0)) return false;  // pairs of 128-column boxes; both halves 16-byte aligned rows
   const ClusterPlan c = tnw == 256 ? plan_cluster<256>(p.K, p.N, swiglu) : plan_cluster<128>(p.K, p.N, swiglu);
   // one tile per cluster: small enough for two CTAs per SM; folded grids run one CTA per SM with a deeper ring
-  return c.smem <= (size_t)(c.tpc == 1 ? 104 : 132) * 1024;
+  return c.smem <= (size_t)132 * 1024;
 }
 
 int cluster_configure() {
@@ -547,10 +581,12 @@ int cluster_configure() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e == cudaSuccess) e = prefer_max_shared(kernel);
   };
-  opt_in(gemv_cluster_kernel<256, 8>);
-  opt_in(gemv_cluster_kernel<256, 16>);
-  opt_in(gemv_cluster_kernel<128, 8>);
-  opt_in(gemv_cluster_kernel<128, 16>);
+  opt_in(gemv_cluster_kernel<256, 8, false>);
+  opt_in(gemv_cluster_kernel<256, 8, true>);
+  opt_in(gemv_cluster_kernel<256, 16, true>);
+  opt_in(gemv_cluster_kernel<128, 8, false>);
+  opt_in(gemv_cluster_kernel<128, 8, true>);
+  opt_in(gemv_cluster_kernel<128, 16, true>);
   if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
   return 0;
 }

@@ -28,7 +28,7 @@ enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2, PRO_ATTN_MERGE 
 struct AttnMerge {
   const float* acc;
   const float* ml;
-  int nclusters;  // 2..16
+  int nclusters;  // 1..8
   int d;          // head dim (a multiple of 128)
   const bf16* gate;  // optional gate logits: element (h, i) at gate[h * gateh_stride + i]
   long gateh_stride;
@@ -65,6 +65,8 @@ struct GemvParams {
   // weight: packed [K/2, N] uint8 (low nibble row j, high nibble row j + K/2), scale [K/group, N]
   const uint8_t* packed;
   const uint32_t* packed_k8;  // optional re-packed copy [K/8, N] words for the streaming kernel
+  const unsigned char* packed_mma;  // optional copy in the tensor-core GEMV's unit order (launch_int4_repack_mma), scales included
+  int mma_pair;                     // that copy pairs gate_proj and up_proj columns (made for EPI_SWIGLU)
   const void* scale;
   int scale_bf16;  // 0: fp32 scales, 1: bf16 scales
   int K, N, group;
@@ -119,6 +121,13 @@ bool cluster_path_ok(const GemvParams& p);
 int cluster_configure();
 int launch_gemv_cluster(const GemvParams& p, int* status, cudaStream_t stream);
 int launch_gemv_stream(const GemvParams& p, int* status, cudaStream_t stream);
+// one activation row on the integer tensor-core instruction (mma.sync m16n8k32), on its own re-packed copy of the weight
+bool mma_path_ok(const GemvParams& p);
+int mma_configure();
+int mma_tile_width(int N);
+size_t mma_repack_bytes(int K, int N, int pair, int scale_bf16);
+int launch_int4_repack_mma(const uint8_t* packed, const void* scale, int scale_bf16, int K, int N, int pair, void* out, cudaStream_t stream);
+int launch_gemv_mma(const GemvParams& p, int* status, cudaStream_t stream);
 // tensor-core (tcgen05) variant for 8..128 activation rows, on the re-packed weight
 bool tc_path_ok(const GemvParams& p);
 int tc_configure();
@@ -126,6 +135,9 @@ int launch_gemm_tc(const GemvParams& p, int* status, cudaStream_t stream);
 // packed [K/2, N] bytes -> [K/8, N] words, word (kb, n) = the nibbles of column n, rows 8kb .. 8kb+7
 int launch_int4_repack_k8(const uint8_t* packed, int K, int N, uint32_t* out, cudaStream_t stream);
 
+// weight [N, K] (bf16 or fp32) -> packed [K/2, N] + scale [K/group, N] fp32, the reference's K-major int4 format
+int launch_int4_quantise(const void* weight, int weight_is_bf16, int N, int K, int group, uint8_t* packed, float* scale,
+                         cudaStream_t stream);
 int launch_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, cudaStream_t stream);
 int launch_int4_dequant(const uint8_t* packed, const void* scale, int scale_bf16, int K, int N, int group, bf16* out,
                         cudaStream_t stream);

@@ -266,9 +266,12 @@ class DecodeEngine:
         tp_rank: int = 0,
         tp_peer_slots: list[int] | None = None,
         prefetch_distance: int | None = None,
+        tensor_core_gemv: bool = True,
     ) -> None:
         """``prefetch_distance``: how many projections ahead the kernels of a batch-1 step ask the L2 cache for
         weights (``dfb_engine_set_prefetch_distance``; ``None`` keeps the library's default, 0 switches it off).
+        ``tensor_core_gemv``: batch 1 runs the layer projections on the integer tensor-core instruction, from one more
+        re-packed copy of each weight (off: the dp4a kernels on the ``k8`` copy).
         ``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
         group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
         cfg = weights.config
@@ -288,7 +291,7 @@ class DecodeEngine:
         self._keep: list = []
         self._captured = False
 
-        def lin(qw: QuantisedWeight) -> Linear:
+        def lin(qw: QuantisedWeight, pair: bool = False, layer_sized: bool = True) -> Linear:
             if not (qw.qweight.is_contiguous() and qw.scale.is_contiguous()):
                 raise ValueError("quantised weights must be contiguous")
             k, n = qw.in_features, qw.out_features
@@ -299,7 +302,13 @@ class DecodeEngine:
 
                 qw.k8 = ops.int4_repack_k8(qw.qweight)
             k8 = qw.k8.data_ptr() if qw.k8 is not None else None
-            return Linear(qw.qweight.data_ptr(), qw.scale.data_ptr(), int(qw.scale.dtype == BF16), k, n, qw.group_size, k8)
+            wants_mma = tensor_core_gemv and layer_sized and self.batch == 1 and not persistent and tp_size == 1 and math == MATH_FAST
+            if wants_mma and qw.group_size == 128 and k % 128 == 0 and (qw.mma is None or qw.mma_pair != pair):
+                from . import ops
+
+                qw.mma, qw.mma_pair = ops.int4_repack_mma(qw.qweight, qw.scale, pair=pair), pair
+            mma = qw.mma.data_ptr() if (wants_mma and qw.mma is not None and qw.mma_pair == pair) else None
+            return Linear(qw.qweight.data_ptr(), qw.scale.data_ptr(), int(qw.scale.dtype == BF16), k, n, qw.group_size, k8, mma, int(pair))
 
         layers = (LayerDesc * len(weights.layers))()
         for i, (lw, cl) in enumerate(zip(weights.layers, cache.layers)):
@@ -307,7 +316,7 @@ class DecodeEngine:
             d = layers[i]
             d.kind = 0 if lw.kind == LINEAR_ATTENTION else 1
             d.input_norm_w, d.post_norm_w = lw.input_norm.data_ptr(), lw.post_norm.data_ptr()
-            d.in_proj, d.out_proj, d.gate_up, d.down = lin(lw.in_proj), lin(lw.out_proj), lin(lw.gate_up), lin(lw.down)
+            d.in_proj, d.out_proj, d.gate_up, d.down = lin(lw.in_proj), lin(lw.out_proj), lin(lw.gate_up, pair=True), lin(lw.down)
             for t in ct.values():
                 if not (t.is_cuda and t.is_contiguous()):
                     raise ValueError("the decode cache must live on the GPU in contiguous tensors")
@@ -331,7 +340,7 @@ class DecodeEngine:
         m.lin_dk, m.lin_dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         m.eps = cfg.rms_norm_eps
         m.inv_freq, m.embed, m.final_norm_w = weights.inv_freq.data_ptr(), weights.embed.data_ptr(), weights.final_norm.data_ptr()
-        m.head = lin(weights.head)
+        m.head = lin(weights.head, layer_sized=False)
         m.layers_host = layers
         m.tokens, m.history, m.pos, m.logits = self.tokens.data_ptr(), self.history.data_ptr(), self.pos.data_ptr(), self.logits.data_ptr()
         m.attn_splits, m.math = self.attn_splits, math

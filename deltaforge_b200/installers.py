@@ -17,8 +17,9 @@ Two granularities:
   leaves the rest of the model alone (the reference's ``install_int4_wide_torch_dequant`` shape,
   kernels/visible_int4_head.py:335-361).
 
-``register_with_reference()`` adds both to the reference's ``REGISTRY`` / ``INSTALLERS`` tables when
-that package is importable, and points the reference's own ``deltaforge::`` ops at these kernels.
+``register_with_reference()`` adds both, and one kernel per reference operation, to the reference's
+``REGISTRY`` / ``INSTALLERS`` / ``CHECK_BUILDERS`` tables when that package is importable, and points the
+reference's own ``deltaforge::`` ops at these kernels.
 """
 
 from __future__ import annotations
@@ -189,33 +190,128 @@ def _forward_to(op):
     return kernel
 
 
+#: kernel name here -> (operation it replaces, the reference's own kernel whose installer performs the module swap and
+#: whose layer-1 checks probe the op, the reference ops that installer's modules call). The per-op kernels are the
+#: reference's module swaps with their ``deltaforge::`` ops answered by ``libdfb200.so``: nothing of the reference's
+#: module code is restated here.
+PER_OP_KERNELS = {
+    "b200_deltanet_step": ("gated_delta_rule", "gated_delta_step", ("delta_rule_step",)),
+    "b200_causal_conv": ("causal_conv", "fused_causal_conv", ("fused_causal_conv_step",)),
+    "b200_attn_decode": ("gqa_attention", "flash_decode_splitkv", ("split_kv_decode_attention", "gqa_decode_attention")),
+    "b200_rmsnorm_residual": ("rms_norm_residual", "fused_rmsnorm_residual", ("add_rms_norm", "rms_norm")),
+    "b200_rope": ("qkv_projection_rope", "fused_rope", ("partial_rope",)),
+    "b200_swiglu": ("swiglu_mlp", "fused_swiglu", ("silu_mul",)),
+}
+
+_redirected: set[str] = set()
+
+
+def redirect_reference_op(op_name: str) -> None:
+    """Register this package's CUDA kernel on the reference's ``deltaforge::<op_name>`` op object (once)."""
+    import importlib
+
+    if op_name in _redirected:
+        return
+    module_name, attr, ours = DROP_IN_OPS[op_name]
+    their_op = getattr(importlib.import_module(module_name), attr)
+    their_op.register_kernel("cuda")(_forward_to(ours))
+    _redirected.add(op_name)
+
+
+def _per_op_installer(ref_kernel: str, op_names: tuple[str, ...]):
+    def installer(model, entry=None) -> None:
+        import importlib
+
+        for op_name in op_names:
+            redirect_reference_op(op_name)
+        importlib.import_module("deltaforge.model").INSTALLERS[ref_kernel](model, entry)
+
+    installer.__name__ = f"install_b200_via_{ref_kernel}"
+    return installer
+
+
+def _per_op_checks(ref_kernel: str, op_names: tuple[str, ...]):
+    def builder(model, **kwargs):
+        import importlib
+
+        for op_name in op_names:
+            redirect_reference_op(op_name)
+        return importlib.import_module("deltaforge.kernels").CHECK_BUILDERS[ref_kernel](model, **kwargs)
+
+    return builder
+
+
+def int4_gemv_checks(model, *, device="cuda", dtype=None, seed: int = 0, replaces: str = "decode_step"):
+    """Layer-1 probes of the int4 GEMV, in the reference's form (src/deltaforge/kernels/quantised_linear.py:737-741,
+    src/deltaforge/harness/correctness.py:136-200): for the narrowest and the widest layer projection, the K = 9216
+    one and the tied head, activations of shape ``(1, 1, K)`` and ``(32, 1, K)``, this package's op against the
+    reference's torch expression on the same packed weight."""
+    import importlib
+
+    check_kernel = importlib.import_module("deltaforge.harness.correctness").check_kernel
+    ref_gemv = importlib.import_module("deltaforge.kernels.visible_int4_head").torch_dequant_gemv_int4
+    ref_quant = importlib.import_module("deltaforge.kernels.tiled_gemv").quantise_int4_k_major
+    linears = [m for m in model.modules() if isinstance(m, nn.Linear)]
+    by_shape = {}
+    for lin in linears:
+        by_shape.setdefault((lin.out_features, lin.in_features), lin)
+    shapes = sorted(by_shape)
+    picks = {shapes[0], shapes[-1], max(shapes, key=lambda nk: nk[1])}
+    probes = [(by_shape[nk].weight, f"N={nk[0]} K={nk[1]}") for nk in sorted(picks)]
+    head = model.embed_tokens.weight if model.config.tie_word_embeddings else model.lm_head.weight
+    probes.append((head, f"N={head.shape[0]} K={head.shape[1]} (lm head)"))
+    gen = torch.Generator(device=device).manual_seed(seed)
+    checks = []
+    for weight, label in probes:
+        qw = ref_quant(weight.detach().to(device))
+        packed, scale, group = qw.qweight, qw.scale, int(qw.group_size)
+        k = weight.shape[1]
+        for shape, note in (((1, 1, k), "batch 1, one token"), ((32, 1, k), "batch 32, one token")):
+            x = torch.randn(shape, device=device, dtype=weight.dtype, generator=gen)
+            checks.append(
+                check_kernel(
+                    f"b200.int4_gemv[{label}]",
+                    lambda a, q, sc, g=group: ref_gemv(a, q, sc, g),
+                    lambda a, q, sc, g=group: ops.tiled_gemv_int4(a, q, sc, g),
+                    args=(x, packed, scale),
+                    replaces=replaces,
+                    note=note,
+                )
+            )
+    return tuple(checks)
+
+
 def register_with_reference(*, redirect_ops: bool = True) -> dict[str, object]:
     """Register this package's kernels with an importable ``deltaforge`` package.
 
-    Adds ``b200_decode_step`` (replaces ``decode_step``) and ``b200_int4_linears`` (replaces
-    ``swiglu_mlp``, the operation the reference's wide int4 installer is filed under) to
-    ``deltaforge.kernels.REGISTRY`` as candidates with their installers in ``deltaforge.model.INSTALLERS``,
-    and, with ``redirect_ops``, registers a CUDA kernel on each of the reference's own ``deltaforge::``
-    op objects so its existing module classes dispatch to ``libdfb200.so`` with no model change.
-    Returns what was registered. Raises ``ImportError`` if the reference is not importable.
+    Adds to ``deltaforge.kernels.REGISTRY`` (as candidates), ``deltaforge.model.INSTALLERS`` and
+    ``deltaforge.kernels.CHECK_BUILDERS``: ``b200_decode_step`` (replaces ``decode_step``), ``b200_int4_linears``
+    (replaces ``swiglu_mlp``, the operation the reference's wide int4 installer is filed under) and one kernel per
+    reference operation (``PER_OP_KERNELS``). With ``redirect_ops`` it also registers a CUDA kernel on each of the
+    reference's own ``deltaforge::`` op objects, so its existing module classes dispatch to ``libdfb200.so`` with no
+    model change. Idempotent. Returns what was registered. Raises ``ImportError`` if the reference is not importable.
     """
     import importlib
 
     kernels = importlib.import_module("deltaforge.kernels")
     ref_model = importlib.import_module("deltaforge.model")
     done: dict[str, object] = {}
-    for name, replaces, installer in (
-        ("b200_decode_step", "decode_step", install_b200_decode_step),
-        ("b200_int4_linears", "swiglu_mlp", install_b200_int4_linears),
-    ):
-        if name not in kernels.REGISTRY._entries:
+    table = [
+        ("b200_decode_step", "decode_step", install_b200_decode_step, lambda model, **kw: int4_gemv_checks(model, replaces="decode_step", **kw)),
+        ("b200_int4_linears", "swiglu_mlp", install_b200_int4_linears, lambda model, **kw: int4_gemv_checks(model, replaces="swiglu_mlp", **kw)),
+    ]  # fmt: skip
+    for name, (replaces, ref_kernel, op_names) in PER_OP_KERNELS.items():
+        table.append((name, replaces, _per_op_installer(ref_kernel, op_names), _per_op_checks(ref_kernel, op_names)))
+    for name, replaces, installer, checks in table:
+        if name not in kernels.REGISTRY:
             kernels.REGISTRY.register(name, installer, replaces=replaces, status="candidate", notes="sm_100a CUDA, libdfb200.so")
         if name not in ref_model.INSTALLERS:
             ref_model.register_installer(name, installer)
+        if name not in kernels.CHECK_BUILDERS:
+            kernels.register_checks(name, checks)
         done[name] = installer
     if redirect_ops:
-        for op_name, (module_name, attr, ours) in DROP_IN_OPS.items():
-            their_op = getattr(importlib.import_module(module_name), attr)
-            their_op.register_kernel("cuda")(_forward_to(ours))
+        for op_name, (_, _, ours) in DROP_IN_OPS.items():
+            redirect_reference_op(op_name)
             done[f"deltaforge::{op_name}"] = ours
     return done

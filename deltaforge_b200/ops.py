@@ -119,12 +119,15 @@ def int4_gemv_fused(
     math: int | None = None,
     force_tiled: bool = False,
     packed_k8: Tensor | None = None,
+    packed_mma: Tensor | None = None,
     op: str = "int4_gemv",
 ) -> Tensor:
     """The general form behind every int4 linear op of this module. Returns ``[..., N]`` bf16.
 
     ``packed_k8`` is the optional re-packed copy of the weight (``int4_repack_k8``); with it, one
     activation row and the FAST arithmetic the streaming kernel runs instead of the register-tiled one.
+    ``packed_mma`` is the optional copy of weight and scales made by ``int4_repack_mma`` (``pair=False``); with
+    it, one activation row and the FAST arithmetic run on the integer tensor-core instruction.
     """
     k, n = _check_int4(x, packed, scale, group_size, op)
     if packed_k8 is not None and (packed_k8.dtype != torch.int32 or tuple(packed_k8.shape) != (k // 8, n)):
@@ -189,6 +192,12 @@ def int4_gemv_fused(
         packed_k8 = packed_k8.contiguous()
         keep.append(packed_k8)
         d.packed_k8 = packed_k8.data_ptr()
+    if packed_mma is not None:
+        want = _lib.load().dfb_int4_repack_mma_bytes(k, n, 0, int(scale.dtype == BF16))
+        if packed_mma.dtype != torch.uint8 or packed_mma.numel() != want or not packed_mma.is_contiguous():
+            raise ValueError(f"{op}: packed_mma must be the {want} contiguous bytes int4_repack_mma(pair=False) returns for this weight")
+        keep.append(packed_mma)
+        d.packed_mma = packed_mma.data_ptr()
     _lib.check(lib.dfb_int4_gemv(C.byref(d), _stream(x)), f"dfb200::{op}")
     return out.reshape(*lead, n)
 
@@ -274,6 +283,29 @@ def int4_repack_k8(packed: Tensor) -> Tensor:
 @int4_repack_k8.register_fake
 def _(packed):
     return packed.new_empty((packed.shape[0] // 4, packed.shape[1]), dtype=torch.int32)
+
+
+def int4_repack_mma(packed: Tensor, scale: Tensor, *, pair: bool = False) -> Tensor:
+    """``packed [K/2, N]`` uint8 and ``scale [K/128, N]`` (fp32 or bf16) -> the bytes the integer tensor-core GEMV
+    streams (``dfb_int4_repack_mma``): one contiguous unit per (column tile, 128-row group) with the group's words in
+    operand-fragment order followed by its scales. ``pair=True`` lays a ``gate_proj|up_proj`` matrix out with each
+    tile holding 128 gate columns and the matching up columns. K must be a multiple of 128."""
+    if packed.dim() != 2 or packed.dtype != torch.uint8:
+        raise ValueError(f"int4_repack_mma: expected uint8 [K/2, N], got {tuple(packed.shape)} {packed.dtype}")
+    half, n = packed.shape
+    k = 2 * half
+    if k % 128 or scale.shape != (k // 128, n) or scale.dtype not in (torch.float32, BF16):
+        raise ValueError(f"int4_repack_mma: K = {k} must be a multiple of 128 with scales [K/128, N] in fp32 or bf16, got {tuple(scale.shape)} {scale.dtype}")
+    if pair and n % 2:
+        raise ValueError("int4_repack_mma: a gate|up pair has an even number of columns")
+    require_cuda(packed, "int4_repack_mma")
+    packed, scale = packed.contiguous(), scale.contiguous()
+    lib = _lib.load()
+    is_bf16 = int(scale.dtype == BF16)
+    out = torch.empty(lib.dfb_int4_repack_mma_bytes(k, n, int(pair), is_bf16), dtype=torch.uint8, device=packed.device)
+    _lib.check(lib.dfb_int4_repack_mma(packed.data_ptr(), scale.data_ptr(), is_bf16, k, n, int(pair), out.data_ptr(), _stream(packed)),
+               "dfb200::int4_repack_mma")  # fmt: skip
+    return out
 
 
 @torch.library.custom_op("dfb200::int4_unpack", mutates_args=())

@@ -44,6 +44,17 @@ int dfb_abi_version(void);
 
 /* ---- int4, group-wise, K-major -------------------------------------------------------------- */
 
+/* Group width along K the format uses for a K-deep weight: 128 when K is a multiple of 256, else one group per half of
+ * K; 0 where the format does not exist (odd K, or a half that is not a power of two). group_size_for,
+ * src/deltaforge/kernels/quantised_linear.py:193-207. */
+int dfb_int4_group_size(int K);
+
+/* weight [N, K] (row-major, bf16 or fp32) -> packed [K/2, N] uint8 + scale [K/group, N] fp32, bit for bit what
+ * quantise_int4_k_major returns (src/deltaforge/kernels/tiled_gemv.py:242-278): symmetric, scale = amax(group) / 7
+ * (1 for an all-zero group), round half to even, clamp to [-7, 7], stored + 8, row j low nibble / row j + K/2 high. */
+int dfb_int4_quantise_k_major(const void* weight, int weight_is_bf16, int N, int K, uint8_t* packed, float* scale,
+                              void* stream);
+
 /* packed [K/2, N] uint8 -> signed values [K, N] int8. The integer half of dequantise_int4_k_major,
  * src/deltaforge/kernels/tiled_gemv.py:284-287. */
 int dfb_int4_unpack(const uint8_t* packed, int K, int N, int8_t* out, void* stream);
@@ -80,6 +91,8 @@ typedef struct dfb_gemv_desc {
   int32_t math;
   int32_t force_tiled; /* 1: use the register-tiled kernel even where the streaming (TMA) kernel applies */
   const void* packed_k8; /* optional: the weight re-packed by dfb_int4_repack_k8; enables the streaming kernel */
+  const void* packed_mma; /* optional: the weight and its scales re-packed by dfb_int4_repack_mma (pair = 0); with one
+                           * activation row and FAST arithmetic the integer tensor-core GEMV runs on it */
 } dfb_gemv_desc;
 
 /* Re-pack a K-major int4 weight for the streaming GEMV: packed [K/2, N] bytes -> out [K/8, N] uint32,
@@ -87,6 +100,17 @@ typedef struct dfb_gemv_desc {
  * 8kb + i. Same values as quantise_int4_k_major produces (src/deltaforge/kernels/tiled_gemv.py:242-278),
  * another order; done once at install time. */
 int dfb_int4_repack_k8(const uint8_t* packed, int K, int N, void* out, void* stream);
+
+/* Re-pack a K-major int4 weight AND its scales for the one-row GEMV on the integer tensor-core instruction
+ * (mma.sync m16n8k32): tiles of 256 columns (128 where N < 4096), one contiguous unit per (tile, 128-row group) holding
+ * the group's words in the order the instruction's operand fragments are read, then the unit's scales. Same values
+ * and scales as quantise_int4_k_major produces (src/deltaforge/kernels/tiled_gemv.py:242-278); columns beyond N are
+ * stored as zeros. pair = 1 lays a gate_proj|up_proj matrix (N = 2 * intermediate) out so that a tile holds 128 gate
+ * columns and the up columns of the same channels (the decode engine fuses SwiGLU on that form). K % 128 == 0.
+ * `out` takes dfb_int4_repack_mma_bytes() bytes, 16-byte aligned. */
+size_t dfb_int4_repack_mma_bytes(int K, int N, int pair, int scale_is_bf16);
+int dfb_int4_repack_mma(const uint8_t* packed, const void* scale, int scale_is_bf16, int K, int N, int pair, void* out,
+                        void* stream);
 
 /* Scratch for one GEMV problem: split-K partial sums, one arrival counter per column tile, and in the
  * last 256 bytes a status word (int32, 0 = ok) that the streaming kernel sets if one of its bounded
@@ -255,6 +279,8 @@ typedef struct dfb_linear {
   int32_t scale_is_bf16;
   int32_t K, N, group;
   const void* packed_k8; /* optional re-packed copy (dfb_int4_repack_k8) */
+  const void* packed_mma; /* optional re-packed copy with scales (dfb_int4_repack_mma); batch-1 steps prefer it */
+  int32_t mma_pair;       /* packed_mma was made with pair = 1 (the gate_up projection) */
 } dfb_linear;
 
 #define DFB_LAYER_DELTANET 0

