@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Workload (``config.workload``): the full Qwen3.5-4B-shaped int4 decode step at batch 1 with a
-4096-token context (BASELINE.json configs[2]), synthetic random-init weights and caches
+4096-token context, synthetic random-init weights and caches
 (``deltaforge_b200.synth``). A "step" is one decode step = one token per sequence, run as one replay of
 the captured CUDA graph. With N > 1 GPUs every rank decodes its own independent sequence (no
 collectives on the data path, weak scaling); the timed region is bracketed by a barrier and a device
@@ -41,11 +41,12 @@ import torch  # noqa: E402
 
 CONTEXT = 4096
 BATCH = 1
-WORKLOAD = "qwen3.5-4b int4 decode step, batch 1, ctx 4096 (BASELINE configs[2])"
+WORKLOAD = "qwen3.5-4b int4 decode step, batch 1, ctx 4096: 32 layers [3 Gated DeltaNet : 1 gated attention], hidden 2560, vocab 248320"
 METRIC = "decode tokens/s (bs1, 4K ctx)"
 
 
 HEAD_GEMV_DRAM_BYTES_PER_LAUNCH = 327_891_968 + 4_020_096  # read + write, mean of two captured launches
+LAYER_GEMV_DRAM_BYTES_PER_LAUNCH = None  # average over the layer projections, from an ncu capture; None until one is taken
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -144,11 +145,12 @@ def cpu_sample_model(head_fraction: int):
     return model, cache, cfg
 
 
-def cpu_step_seconds(model, cache, head_fraction: int, repeats: int) -> list[float]:
-    """Seconds for one whole-token equivalent, measured ``repeats`` times on the sample model.
+def cpu_step_seconds(model, cache, head_fraction: int, repeats: int, whole: bool) -> list[float]:
+    """Seconds for one token, measured ``repeats`` times on the sample model.
 
-    One sample pass = 1 DeltaNet layer + 1 attention layer (ctx 4096) + 1/head_fraction of the LM head.
-    Layers are timed separately so a token is 24 x DeltaNet + 8 x attention + head_fraction x head slice."""
+    ``whole``: a token's worth of work is actually executed, the DeltaNet sample layer 24 times, the attention sample
+    layer (ctx 4096) 8 times and the 1/head_fraction slice of the LM head head_fraction times, and timed as one
+    region. Otherwise one pass over each is timed and scaled (24x, 8x, head_fraction x): an extrapolation."""
     from oracle import ref_ops as R
 
     tok = torch.zeros((BATCH, 1), dtype=torch.long)
@@ -158,6 +160,17 @@ def cpu_step_seconds(model, cache, head_fraction: int, repeats: int) -> list[flo
         h = model.embed_tokens(tok)
         pos = torch.full((BATCH, 1), CONTEXT)
         cos, sin = R.rope_cos_sin(pos, model.inv_freq, h.dtype)
+        if whole:
+            t0 = time.perf_counter()
+            for _ in range(24):
+                h = model.layers[0](h, cos, sin, cache, CONTEXT)
+            for _ in range(8):
+                h = model.layers[1](h, cos, sin, cache, CONTEXT)
+            hn = R.rms_norm(h, model.norm.weight, model.norm.eps)
+            for _ in range(head_fraction):
+                model.project_logits(hn)
+            out.append(time.perf_counter() - t0)
+            continue
         t0 = time.perf_counter()
         h1 = model.layers[0](h, cos, sin, cache, CONTEXT)
         t1 = time.perf_counter()
@@ -182,34 +195,36 @@ def usable_host_cores() -> int:
 
 
 def run_cpu_port(steps: int, warmup: int, budget_s: float) -> dict:
-    """Time the CPU port for ``steps`` steps after ``warmup``; the sample shrinks to fit ``budget_s``."""
+    """Time the CPU port for ``steps`` steps after ``warmup``. Whole tokens are executed when that fits ``budget_s``;
+    otherwise one pass over the sample is timed per step and scaled, and the result says ``extrapolated``."""
     # torchrun pins OMP_NUM_THREADS to 1; this arm runs on one rank alone and takes every host core
     torch.set_num_threads(max(torch.get_num_threads(), usable_host_cores()))
     threads = torch.get_num_threads()
     head_fraction = 8
     model, cache, _ = cpu_sample_model(head_fraction)
+    region_t0 = time.perf_counter()
     with torch.no_grad():
-        first = cpu_step_seconds(model, cache, head_fraction, 1)[0]  # also first-touches the temporaries
-        probe_t0 = time.perf_counter()
-        cpu_step_seconds(model, cache, head_fraction, 1)
-        per_pass = time.perf_counter() - probe_t0
-        if per_pass * (steps + warmup) > budget_s and head_fraction < 64:
-            head_fraction = 64
-            model, cache, _ = cpu_sample_model(head_fraction)
-            cpu_step_seconds(model, cache, head_fraction, 1)
-        cpu_step_seconds(model, cache, head_fraction, max(0, warmup - 1))
-        times = cpu_step_seconds(model, cache, head_fraction, steps)
+        first = cpu_step_seconds(model, cache, head_fraction, 1, whole=False)[0]  # also first-touches the temporaries
+        estimate = cpu_step_seconds(model, cache, head_fraction, 1, whole=False)[0]
+        whole = estimate * (steps + warmup) <= budget_s
+        cpu_step_seconds(model, cache, head_fraction, max(0, warmup - (0 if whole else 1)), whole)
+        times = cpu_step_seconds(model, cache, head_fraction, steps, whole)
     sec = sum(times) / len(times)
+    work = "the DeltaNet sample layer 24 times, the attention sample layer (ctx %d) 8 times, the LM head in %d column slices" % (CONTEXT, head_fraction)
     return {
         "value": BATCH / sec,
         "unit": "tokens/s",
         "cores": threads,
         "kind": "port",
+        "extrapolated": not whole,
         "sample": (
-            f"per step: 1 DeltaNet layer + 1 full-attention layer (ctx {CONTEXT}) + 1/{head_fraction} of the LM head columns "
-            f"through oracle/ (torch CPU, {threads} threads), scaled to 24 + 8 layers + whole head; {steps} timed passes"
+            (f"per step one token's worth of work is executed and timed as a whole: {work}" if whole else
+             f"per step ONE pass over a DeltaNet layer, an attention layer (ctx {CONTEXT}) and 1/{head_fraction} of the LM head is timed "
+             f"and scaled to 24 + 8 layers + the whole head")
+            + f"; a two-layer model at the benchmark's widths through oracle/ (torch CPU, {threads} threads); {steps} timed steps"
         ),
         "seconds_per_token": sec,
+        "timed_seconds": time.perf_counter() - region_t0,
         "first_pass_seconds": first,
     }
 
@@ -343,6 +358,29 @@ def run_ours(args) -> dict | None:
 
     head_ms, head_bytes = time_head_gemv(weights) if rank == 0 else (0.0, 0)
     launches_per_step, attn_splits = eng.launches_per_step, eng.attn_splits
+    proj_stats = None
+    if rank == 0 and args.engine == "graph":
+        # After every timed region: re-capture the step with the kernels' per-CTA timestamp marks on, run a few tokens, and
+        # read the last one launch by launch. A launch's time is its share of the step's critical path: from the last
+        # exit of the launch before it to its own last exit.
+        from deltaforge_b200 import timeline as TL
+
+        cache.restore(snap)
+        trace = eng.set_trace()
+        eng.decode(tok, 4)
+        torch.cuda.synchronize()
+        rows = TL.summarise(trace, TL.launch_names(list(cfg.layer_types), launches_per_step))
+        eng.set_trace(0)
+        if args.timeline:
+            Path(args.timeline).write_text(TL.render(rows) + "\n")
+        proj = [r for r in rows if r["name"].split(".")[-1] in ("in_proj", "out_proj", "gate_up", "down") and "chain" in r and "boundary" in r]
+        if proj:
+            layer_bytes = sum(
+                q.qweight.numel() + q.scale.numel() * q.scale.element_size() + 2 * q.out_features
+                for L in weights.layers for q in (L.in_proj, L.out_proj, L.gate_up, L.down)
+            )  # fmt: skip
+            proj_stats = {"launches": len(proj), "us": sum(r["chain"] + r["boundary"] for r in proj),
+                          "bytes": layer_bytes * len(proj) / (4 * len(weights.layers))}  # fmt: skip
     tp_line = None
     if dist is not None and not args.no_tp_arm and BATCH == 1:
         # the multi-GPU run also reports the tensor-parallel form of the same model on the same GPUs
@@ -354,18 +392,6 @@ def run_ours(args) -> dict | None:
             tp_line = {"n": world, "error": f"{type(exc).__name__}: {exc}"[:400]}
     if rank != 0:
         return None
-    if args.timeline and args.engine == "graph" and tp_line is None:
-        # after every timed region: re-capture the step with the per-CTA timestamp marks on, run a few tokens, and
-        # write one row per launch of the last one
-        from deltaforge_b200 import timeline as TL
-
-        cache.restore(snap)
-        trace = eng.set_trace()
-        eng.decode(tok, 4)
-        torch.cuda.synchronize()
-        rows = TL.summarise(trace, TL.launch_names(list(cfg.layer_types), eng.launches_per_step))
-        Path(args.timeline).write_text(TL.render(rows) + "\n")
-        eng.set_trace(0)
     peak, peak_kind = measured_peaks()
     bytes_step = decode_bytes_per_step(cfg, batch=BATCH, context=CONTEXT, scale_bytes=2)
     ms_per_step = ms_max / steps
@@ -406,8 +432,9 @@ def run_ours(args) -> dict | None:
         "gpu_launches": steps * launches_per_step,
         "launches_per_step": launches_per_step,
         "clocks": clocks.summary(),
-        "roofline": {
-            "kernel": "gemv_stream_kernel (int4 GEMV, RMSNorm prologue) on the LM head 248320x2560",
+        "roofline": None,
+        "roofline_head": {
+            "kernel": "gemv_stream_kernel (int4 GEMV, RMSNorm prologue) on the LM head 248320x2560, timed alone with CUDA events",
             "bound": "hbm",
             "achieved": head_gbs,
             "peak": peak,
@@ -416,8 +443,8 @@ def run_ours(args) -> dict | None:
             "peak_kind": f"of {peak_kind}",
             "bytes_per_launch": head_bytes,
             "us_per_launch": head_ms * 1e3,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this matrix, from the ncu
-            # capture summarised in profiles/gemv_stream_kernel_lm_head.md (not re-measured by this run)
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this matrix, from an ncu capture of
+            # the same launch (a record of that capture, not re-measured by this run)
             "traffic": HEAD_GEMV_DRAM_BYTES_PER_LAUNCH,
         },
         "roofline_step": {
@@ -432,6 +459,26 @@ def run_ours(args) -> dict | None:
         },
         "finite_logits": finite,
     }
+    if proj_stats is not None:
+        # the dominant kernel family: the int4 GEMV of the 128 layer projections (4 launches per layer)
+        gbs = proj_stats["bytes"] / (proj_stats["us"] * 1e-6) / 1e9
+        line["roofline"] = {
+            "kernel": "layer-projection int4 GEMV (gemv_mma_kernel / gemv_cluster_kernel), all launches of one token",
+            "bound": "hbm",
+            "achieved": gbs,
+            "peak": peak,
+            "unit": "GB/s",
+            "frac": gbs / peak,
+            "peak_kind": f"of {peak_kind}",
+            "launches": proj_stats["launches"],
+            "bytes_per_launch": proj_stats["bytes"] / proj_stats["launches"],
+            "us_per_launch": proj_stats["us"] / proj_stats["launches"],
+            "timed_by": "device timestamps (%globaltimer) recorded by the kernels in a traced replay of the same graph: a launch's "
+            "time is its share of the step's critical path, from the previous launch's last exit to its own last exit",
+            "traffic": LAYER_GEMV_DRAM_BYTES_PER_LAUNCH,
+        }
+    else:
+        line["roofline"] = line["roofline_head"]
     if tp_line is not None:
         line["tp"] = tp_line
     return line
@@ -516,7 +563,7 @@ def tp_arm(dist, rank: int, world: int, dev, steps: int, warmup: int, layers: in
 
 
 def run_tp(args) -> dict | None:
-    """All ranks of the job form ONE tensor-parallel replica decoding one batch (BASELINE configs[4])."""
+    """All ranks of the job form ONE tensor-parallel replica decoding one batch."""
     from deltaforge_b200 import engine as E
     from deltaforge_b200 import qwen3_5_4b_config, synth
     from deltaforge_b200 import tp as TP
@@ -634,7 +681,18 @@ def main() -> None:
             "vs_baseline": None,
             "dtype": "int4 weights dequantised to bf16, fp32 matmul (the reference's torch expression)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "context": CONTEXT},
+            "config": {
+                "workload": WORKLOAD,
+                "batch_per_gpu": BATCH,
+                "context": CONTEXT,
+                "sequences": BATCH,
+                "parallelism": "host cores of rank 0 only",
+                "l2": "not applicable (CPU arm)",
+                "engine": "oracle port on the CPU",
+                "attn_splits": None,
+                "scale_dtype": "fp32",
+            },
+            "extrapolated": res["extrapolated"],
             "cpu_baseline": res,
             "e2e": {"value": res["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,

@@ -35,7 +35,7 @@ namespace {
 constexpr int AW = 8;  // warps per CTA
 constexpr int D = 256;
 constexpr int MAX_CS = 8;
-constexpr int MAX_KEYS = 160;  // rows per slice (160 KB of staged K and V, one CTA per SM)
+constexpr int MAX_KEYS = 160;  // most rows a slice may have (160 KB of staged K and V: one CTA per SM)
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -123,9 +123,11 @@ __device__ __noinline__ void norm_rope_row(const bf16* src, const bf16* nw, floa
 template <int GROUPS>
 __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams p) {
   extern __shared__ __align__(128) unsigned char smraw[];
-  bf16* kst = (bf16*)smraw;                       // [MAX_KEYS][D] staged keys
-  bf16* vst = kst + MAX_KEYS * D;                 // [MAX_KEYS][D] staged values
-  float* q_s = (float*)(vst + MAX_KEYS * D);      // [GROUPS][D] rotated queries times the softmax scale
+  // rows staged per slice: what the cache's capacity can ask for (at least the 32 rows' worth of bytes the warp merge reuses)
+  const int cap = max((p.max_seq + (int)gridDim.x - 1) / (int)gridDim.x, AW * GROUPS * 2);
+  bf16* kst = (bf16*)smraw;                       // [cap][D] staged keys
+  bf16* vst = kst + cap * D;                      // [cap][D] staged values
+  float* q_s = (float*)(vst + cap * D);           // [GROUPS][D] rotated queries times the softmax scale
   float* rowbuf = q_s + GROUPS * D;               // [2][D] scratch for the new key / value row
   float* ml_s = rowbuf + 2 * D;                   // [AW][GROUPS][2]
   float* cl_acc = ml_s + AW * GROUPS * 2;         // [MAX_CS][GROUPS][D] per-rank sums (used in rank 0)
@@ -403,8 +405,9 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
 }
 
 template <int GROUPS>
-size_t step_smem() {
-  const size_t stage = (size_t)2 * MAX_KEYS * D * 2;  // also holds the [AW][GROUPS][D] float warp-merge buffer
+size_t step_smem(int max_seq = MAX_KEYS, int splits = 1) {
+  const int cap = std::max((max_seq + splits - 1) / splits, AW * GROUPS * 2);
+  const size_t stage = (size_t)2 * cap * D * 2;  // also holds the [AW][GROUPS][D] float warp-merge buffer
   const size_t merge = (size_t)AW * GROUPS * D * 4;
   return std::max(stage, merge) +
          (size_t)(GROUPS * D + 2 * D + AW * GROUPS * 2 + MAX_CS * GROUPS * D + MAX_CS * GROUPS * 2 + GROUPS * 16 + 32 + GROUPS * 2) * 4 + 16 + 128;
@@ -415,7 +418,7 @@ int launch_groups(const AttnStepParams& p, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.splits, p.hkv, p.batch);
   cfg.blockDim = dim3(AW * 32, 1, 1);
-  cfg.dynamicSmemBytes = step_smem<GROUPS>();
+  cfg.dynamicSmemBytes = step_smem<GROUPS>(p.max_seq, p.splits);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

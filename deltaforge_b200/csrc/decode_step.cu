@@ -279,8 +279,10 @@ struct Engine {
   // partial results are merged by the output projection while it builds its activation, not by a last-arriver
   // protocol through global memory at the end of the attention kernel.
   int attn_cluster_size() const {
+    // small clusters schedule sooner; at most 8 clusters per KV head, so that the output projection can merge them
+    // (up to 16 where the last cluster to arrive merges: 128 slices of a long cache)
     int c = std::min(m.attn_splits, 4);
-    while (c < 8 && m.attn_splits / c > 16) c *= 2;
+    while (c < 8 && m.attn_splits / c > 8) c *= 2;
     return c;
   }
   bool attn_defer_merge(const dfb_layer_desc& L) const {

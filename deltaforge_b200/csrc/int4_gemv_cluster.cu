@@ -364,7 +364,6 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
       if (i > 0) consumer_sync<CT>();  // the previous tile's row-lane sums have been read
       *(float4*)(red + rl * TNW + cq * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
       consumer_sync<CT>();
-      if (t == 0 && i + 1 == ntiles) trace_mark(p.trace, cta, 4);
       if (t < TNW) {
         float v = 0.f;
 #pragma unroll

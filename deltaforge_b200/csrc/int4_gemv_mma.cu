@@ -329,6 +329,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
           if (lane == 0) mbar_arrive(&empty[st]);
         }
       }
+      if (s == 0 && t == 0) trace_mark(p.trace, cta, 4);  // the first unit is done: what follows is the steady state
       if (++st == a.stages) st = 0, phase ^= 1;
     }
     if (!ok && lane == 0) atomicExch(a.status, 4);
@@ -344,7 +345,6 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
         dsmem_store(dsm + rank * TN + col + 8, 0, tot[b][1]);
       }
     }
-    if (t == 0) trace_mark(p.trace, cta, 4);
   }
   if (cs > 1) cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
   else __syncthreads();

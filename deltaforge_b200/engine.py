@@ -239,8 +239,10 @@ def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: i
     while splits < 128 and -(-max_seq_len // splits) > 160:
         splits *= 2
     if batch <= 2 and -(-max_seq_len // splits) <= 160:
-        while splits * 2 * batch * kv_heads <= sm_count and max_seq_len // (splits * 2) >= 64:
-            splits *= 2  # short caches: still use the SMs
+        # shorter slices while the grid still fits the GPU in one go (a slice's staging buffer shrinks with it, so two or
+        # three CTAs share an SM): the scan of a slice is the long pole of the kernel
+        while splits * 2 <= 128 and splits * 2 * batch * kv_heads <= 2 * sm_count and max_seq_len // (splits * 2) >= 64:
+            splits *= 2
         return splits
     # longer caches take the two-kernel path, which has no slice limit: about eight waves of CTAs, slices of
     # at least 256 keys (the tensor-core kernel streams 16-key tiles through a ring and wants a long slice)

@@ -58,6 +58,7 @@ def summarise(trace: torch.Tensor, names: list[str]) -> list[dict]:
             "issued": col(7, "med"),
             "wait_ret": col(1, "med"),
             "x_ready": col(2, "med"),
+            "unit1_done": col(4, "med"),
             "dots_done": col(3, "med"),
             "dots_done_last": col(3, "max"),
             "barrier": col(5, "med"),
@@ -74,7 +75,7 @@ def summarise(trace: torch.Tensor, names: list[str]) -> list[dict]:
 
 
 def render(rows: list[dict]) -> str:
-    cols = ("launch", "name", "ctas", "entry_first", "entry_last", "issued", "wait_ret", "x_ready", "dots_done", "dots_done_last",
+    cols = ("launch", "name", "ctas", "entry_first", "entry_last", "issued", "wait_ret", "x_ready", "unit1_done", "dots_done", "dots_done_last",
             "barrier", "exit_last", "boundary", "chain")  # fmt: skip
     out = [" ".join(f"{c:>14}" for c in cols)]
     for r in rows:

@@ -332,8 +332,18 @@ class TensorParallelEngine:
         eng._set_tokens(tokens)
         if graph and self._warm:
             if self._graph is None:
+                # Recording collectives into a CUDA graph is something only NCCL can do: any other backend moves the data
+                # through the host and synchronises the stream, which a capturing stream refuses, and the rank that gets
+                # that error leaves its peers waiting inside their next collective.
+                if self.dist.get_backend(self.group) != "nccl":
+                    raise ValueError("graph=True records the all-reduces into a CUDA graph and needs the NCCL backend")
+                # Every rank enters the capture together, with nothing of the warm step still queued, and the capture is
+                # thread-local: NCCL's watchdog thread polls CUDA events, which under the default (global) mode
+                # invalidates a capture in progress on one rank only, again leaving the others waiting.
+                torch.cuda.synchronize(eng.device)
+                self.dist.barrier(group=self.group)
                 self._graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(self._graph):  # recorded, not executed
+                with torch.cuda.graph(self._graph, capture_error_mode="thread_local"):  # recorded, not executed
                     self._run()
             self._graph.replay()
         else:

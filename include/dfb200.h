@@ -403,8 +403,8 @@ int dfb_engine_set_prefetch_distance(void* engine, int distance);
 /* Profiling of the graph-of-kernels step: with `buffer` (device memory, max_launches * ctas_per_launch * 8
  * int64, zeroed by the caller) set, one thread of every CTA of launch number l of a step stores %globaltimer
  * (ns) at buffer[(l * ctas_per_launch + cta) * 8 + mark]; marks: 0 kernel entry, 1 the wait for the previous
- * kernel returned, 2 activation ready in shared memory, 3 dot products done (all weights arrived), 4 CTA-level
- * sums done, 5 cluster barrier passed, 6 exit, 7 this CTA's copies (and prefetches) issued. NULL switches it
+ * kernel returned, 2 activation ready in shared memory, 3 dot products done (all weights arrived), 4 the first
+ * unit of weights done, 5 cluster barrier passed, 6 exit, 7 this CTA's copies (and prefetches) issued. NULL switches it
  * off. Applies to steps enqueued or captured afterwards. */
 int dfb_engine_set_trace(void* engine, int64_t* buffer, int max_launches, int ctas_per_launch);
 /* Number of kernel launches in one step. */

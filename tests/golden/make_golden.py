@@ -19,7 +19,9 @@ from pathlib import Path
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF_SRC = os.environ.get("DELTAFORGE_REFERENCE_SRC", "/root/reference/src")
+REF_SRC = os.environ.get("DELTAFORGE_REFERENCE_SRC")
+if not REF_SRC:
+    raise SystemExit("set DELTAFORGE_REFERENCE_SRC to the `src` directory of a LoveManna/deltaforge checkout")
 sys.path.insert(0, REF_SRC)
 
 from deltaforge import reference as ref  # noqa: E402

@@ -48,7 +48,7 @@ def kl_and_agreement(ref_logits: torch.Tensor, cand_logits: torch.Tensor) -> tup
 
 
 def test_lm_head_at_full_size_against_the_oracle():
-    """BASELINE configs[0]: all 248320 columns, bf16 scales, RMSNorm prologue, through the streaming kernel."""
+    """The LM-head configuration: all 248320 columns, bf16 scales, RMSNorm prologue, through the streaming kernel."""
     k, n = 2560, 248320
     g = torch.Generator().manual_seed(2024)
     packed = torch.randint(0, 256, (k // 2, n), generator=g, dtype=torch.uint8)
@@ -98,7 +98,7 @@ def full_model():
 
 
 def test_32_layer_step_with_a_4096_token_cache_against_the_oracle(full_model):
-    """BASELINE configs[2], teacher-forced for 32 positions, FAST and EXACT arithmetic."""
+    """The benchmarked configuration, teacher-forced for 32 positions, FAST and EXACT arithmetic."""
     cfg, weights = full_model
     context, positions = 4096, 32
     max_seq = context + positions + 8
@@ -150,7 +150,7 @@ def test_32_layer_step_with_a_4096_token_cache_against_the_oracle(full_model):
 
 
 def test_batch_32_with_a_16k_token_cache_against_the_oracle():
-    """BASELINE configs[3] on a 4-layer cut (one full-attention layer): 32 sequences, 16384 cached tokens each, so
+    """The many-sequence configuration on a 4-layer cut (one full-attention layer): 32 sequences, 16384 cached tokens each, so
     the engine takes the tensor-core projections and the tensor-core split-KV decode kernel."""
     from deltaforge_b200.config import ModelConfig, hybrid_layer_types
 
