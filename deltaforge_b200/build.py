@@ -16,8 +16,11 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-LIB = PKG / "libdfb200.so"
-STAMP = PKG / "libdfb200.so.stamp"
+# DFB200_BOUNDS_BUILD=1 (or `python -m deltaforge_b200.build --bounds`) selects the variant compiled with -DDFB_BOUNDS,
+# whose kernels check their store and tile indices and report through the status word instead of making a bad access
+BOUNDS = os.environ.get("DFB200_BOUNDS_BUILD") == "1" or "--bounds" in sys.argv
+LIB = PKG / ("libdfb200_bounds.so" if BOUNDS else "libdfb200.so")
+STAMP = PKG / (LIB.name + ".stamp")
 
 NVCC_FLAGS = [
     "-gencode",
@@ -28,6 +31,7 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
     "-shared",
+    *(["-DDFB_BOUNDS"] if BOUNDS else []),
 ]
 
 

@@ -147,8 +147,11 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   const int L = pos + 1;
   const int chunk = (L + S - 1) / S;  // <= MAX_KEYS, checked on the host against the cache capacity
   const int k_begin = split * chunk, k_end = min(L, k_begin + chunk);
-  const bool owns_new = (k_begin <= pos) && (pos < k_end);
-  const int n_old = max(0, (owns_new ? k_end - 1 : k_end) - k_begin);  // rows already in the cache
+  // (bounds build: a slice longer than its staging buffer is recorded and scanned as empty; the CTA still takes part in
+  // every barrier)
+  const bool sane = DFB_IN_BOUNDS(chunk <= max((p.max_seq + S - 1) / S, AW * GROUPS * 2), p.status, 6);
+  const bool owns_new = sane && (k_begin <= pos) && (pos < k_end);
+  const int n_old = sane ? max(0, (owns_new ? k_end - 1 : k_end) - k_begin) : 0;  // rows already in the cache
   const int n_keys = n_old + (owns_new ? 1 : 0);
 
   if (t == 0) {

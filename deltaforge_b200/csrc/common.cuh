@@ -91,6 +91,20 @@ __device__ __forceinline__ void trace_mark(const Trace& tr, int cta, int phase) 
   }
 }
 
+// Bounds build (nvcc -DDFB_BOUNDS, `python -m deltaforge_b200.build --bounds`): the kernels check the indices of
+// their stores and of their shared-memory tiles against the extents and, instead of making the access, record
+// code 60 + site in the status word the launch was given. The checks compile to nothing in the normal build. It
+// stands in for a memory checker on machines where none can be run.
+#ifdef DFB_BOUNDS
+#define DFB_IN_BOUNDS(cond, status_ptr, site) dfb_in_bounds((cond), (status_ptr), (site))
+__device__ __forceinline__ bool dfb_in_bounds(bool ok, int* status, int site) {
+  if (!ok && status != nullptr) atomicCAS(status, 0, 60 + site);
+  return ok;
+}
+#else
+#define DFB_IN_BOUNDS(cond, status_ptr, site) true
+#endif
+
 // Error reporting shared by the C entry points (defined in abi.cu).
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);

@@ -116,6 +116,7 @@ __device__ __forceinline__ EpiPre epilogue_preload(const GemvParams& p, int r, i
 
 // Output element (r, n) from its fp32 sum; returns the value stored (as fp32).
 __device__ __forceinline__ float epilogue_store_pre(const GemvParams& p, int r, int n, float sum, const EpiPre& pre) {
+  if (!DFB_IN_BOUNDS(r >= 0 && r < p.rows && n >= 0 && n < p.N, p.status, 1)) return 0.f;
   if (p.epilogue == EPI_PARTIAL_PEER) {
     // one 8-byte store per rank: the value and the epoch arrive together, the receiver needs no fence
     const unsigned epoch = *p.peer.epoch_ctr * 256u + (unsigned)p.peer.epoch_off;

@@ -305,6 +305,7 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
       for (int s = 0; s < nunits; ++s) {
         if (ok) ok = mbar_wait(&full[st], phase);
         if (ok) {
+          if (!DFB_IN_BOUNDS(st < a.stages && s < a.max_units && i < a.tpc, a.status, 5)) break;
           const unsigned char* wbase = ring + (size_t)st * STAGE;
           // even rows of a word sit in the low nibbles of its bytes, odd rows in the high nibbles: the odd rows are
           // used where they are (16 x their value) in accumulators of their own, and shifted once per group

@@ -183,13 +183,16 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
     if (t == 0) trace_mark(p.trace, cta, 1);
     // Everything this CTA reads that an earlier kernel wrote goes in flight at once.
-    uint2 xraw = make_uint2(0u, 0u), wraw = make_uint2(0u, 0u);
-    if (warp < nunits && p.prologue != PRO_ATTN_MERGE) {
-      const int k = (g0 + warp) * 128 + lane * 4;
-      xraw = *(const uint2*)(p.x + k);
-      if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
-      if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
-    }
+    // (the first two groups each warp quantises: a CTA holds at most sixteen groups in practice, so this is all of them)
+    uint2 xraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)}, wraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if (warp + j * CW < nunits && p.prologue != PRO_ATTN_MERGE) {
+        const int k = (g0 + warp + j * CW) * 128 + lane * 4;
+        xraw[j] = *(const uint2*)(p.x + k);
+        if (p.prologue == PRO_RMSNORM) wraw[j] = *(const uint2*)(p.norm_w + k);
+        if (p.prologue == PRO_SILU_MUL) wraw[j] = *(const uint2*)(p.up + k);
+      }
     const int my_n = t < TN ? tile_column<TN>(tile, t, p.N, 0) : -1;
     if ((cs == 1 || rank == 0) && !swiglu && my_n >= 0) pre = epilogue_preload(p, 0, my_n);
     float rstd = 1.f;
@@ -216,19 +219,20 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
     for (int gl = warp; gl < nunits; gl += CW) {
       const int g = g0 + gl;
       float v[4];
-      if (gl != warp && p.prologue != PRO_ATTN_MERGE) {
+      uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
+      if (gl >= warp + 2 * CW && p.prologue != PRO_ATTN_MERGE) {  // a third group and later: loaded here
         const int k = g * 128 + lane * 4;
-        xraw = *(const uint2*)(p.x + k);
-        if (p.prologue == PRO_RMSNORM) wraw = *(const uint2*)(p.norm_w + k);
-        if (p.prologue == PRO_SILU_MUL) wraw = *(const uint2*)(p.up + k);
+        xv = *(const uint2*)(p.x + k);
+        if (p.prologue == PRO_RMSNORM) wv = *(const uint2*)(p.norm_w + k);
+        if (p.prologue == PRO_SILU_MUL) wv = *(const uint2*)(p.up + k);
       }
       if (p.prologue == PRO_ATTN_MERGE) {
         attn_merge_values(p.merge, g * 128 + lane * 4, v);
       } else {
-        const float xr[4] = {__uint_as_float(xraw.x << 16), __uint_as_float(xraw.x & 0xffff0000u), __uint_as_float(xraw.y << 16),
-                             __uint_as_float(xraw.y & 0xffff0000u)};
-        const float wr[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xffff0000u), __uint_as_float(wraw.y << 16),
-                             __uint_as_float(wraw.y & 0xffff0000u)};
+        const float xr[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16),
+                             __uint_as_float(xv.y & 0xffff0000u)};
+        const float wr[4] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
+                             __uint_as_float(wv.y & 0xffff0000u)};
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
       }
@@ -284,28 +288,44 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
     const int gq = lane >> 2, tq = lane & 3;
     const int mul0 = tq == 0 ? 1 : (tq == 1 ? 65536 : 0), mul1 = tq == 0 ? 256 : 0;
     float tot[NB][2] = {};
+    // With every unit of this CTA resident (nothing is recycled) all arrivals are awaited first: no barrier instruction
+    // then sits between the units, and one unit's loads overlap the arithmetic of the unit before.
+    const bool resident = a.stages >= nunits;
+    if (resident)
+      for (int s = 0; s < nunits; ++s)
+        if (ok) ok = mbar_wait(&full[s], 0);
     int st = 0, phase = 0;
     for (int s = 0; s < nunits; ++s) {
-      if (ok) ok = mbar_wait(&full[st], phase);
+      if (!resident && ok) ok = mbar_wait(&full[st], phase);
       if (ok) {
+        if (!DFB_IN_BOUNDS(st < a.stages && s < a.max_units, a.status, 2)) break;
         const unsigned char* ub = ring + (size_t)st * a.unit_bytes;
         const uint2* xrow = (const uint2*)(xb + (size_t)s * XB_BYTES);
-        int c[NB][4] = {};
+        // everything the unit needs from shared memory goes in flight at once; the two halves of the group's rows get
+        // accumulators of their own, so that only two mma depend on one another
+        uint4 w[2][NB];
+        uint2 bv[4];
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-          uint4 w[NB];
+        for (int pr = 0; pr < 2; ++pr)
 #pragma unroll
-          for (int b = 0; b < NB; ++b) w[b] = *(const uint4*)(ub + (size_t)(NB * warp + b) * 1024 + (pr * 32 + lane) * 16);
+          for (int b = 0; b < NB; ++b) w[pr][b] = *(const uint4*)(ub + (size_t)(NB * warp + b) * 1024 + (pr * 32 + lane) * 16);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint2 bv = xrow[((2 * pr + h) * 4 + tq) * 8 + gq];
+        for (int ks = 0; ks < 4; ++ks) bv[ks] = xrow[(ks * 4 + tq) * 8 + gq];
+        int ch[2][NB][4] = {};
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr)
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-              const uint32_t wa = h ? w[b].z : w[b].x, wb = h ? w[b].w : w[b].y;  // columns gq and gq + 8
-              imma(c[b], wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, wa & 0xF0F0F0F0u, wb & 0xF0F0F0F0u, bv.x, bv.y);
+              const uint32_t wa = h ? w[pr][b].z : w[pr][b].x, wb = h ? w[pr][b].w : w[pr][b].y;  // columns gq and gq + 8
+              imma(ch[pr][b], wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, wa & 0xF0F0F0F0u, wb & 0xF0F0F0F0u, bv[2 * pr + h].x, bv[2 * pr + h].y);
             }
-          }
-        }
+        int c[NB][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) c[b][i] = ch[0][b][i] + ch[1][b][i];
         const float f = fg[s];
         const int zp = tq == 0 ? 128 * msum[s] : 0;  // the zero point: 16 * 8 * sum m, taken off where piece 0 lives
 #pragma unroll
@@ -341,6 +361,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
       tot[b][1] += __shfl_xor_sync(0xffffffffu, tot[b][1], 1);
       if (tq == 0) {
         const int col = (NB * warp + b) * 16 + gq;
+        if (!DFB_IN_BOUNDS(rank < cs && col + 8 < TN, a.status, 3)) continue;
         dsmem_store(dsm + rank * TN + col, 0, tot[b][0]);
         dsmem_store(dsm + rank * TN + col + 8, 0, tot[b][1]);
       }
@@ -359,7 +380,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
       red[t] = v;
       asm volatile("bar.sync 2, %0;" ::"n"(TN) : "memory");
       const int ch = tile * (TN / 2) + t;
-      if (t < TN / 2 && ch < p.N / 2) {
+      if (t < TN / 2 && ch < p.N / 2 && DFB_IN_BOUNDS(ch >= 0, a.status, 4)) {
         const float sv = round_bf16(silu_f(round_bf16(red[t])));
         p.out[ch] = f2bf(__fmul_rn(sv, round_bf16(red[t + TN / 2])));
       }

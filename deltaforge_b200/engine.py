@@ -407,7 +407,8 @@ class DecodeEngine:
         if code.value:
             raise _lib.Dfb200Error(
                 f"a decode kernel reported status {code.value}: a bounded wait ran out "
-                "(50: a tensor-parallel peer's partial sums never arrived; other codes: an asynchronous copy)"
+                "(50: a tensor-parallel peer's partial sums never arrived; 60 and up: an index check of the bounds build; "
+                "other codes: an asynchronous copy)"
             )
 
     def _stream(self) -> int:
