@@ -351,6 +351,15 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
       }
     }
     if (p.defer_merge) {  // the output projection merges the clusters' partial results while it builds its activation
+      if (cidx == 0 && p.attn_output_gate) {
+        // ... and multiplies by the output gate, which one cluster per KV head leaves in `out` already activated:
+        // bf16(sigmoid(fp32(gate))) (src/deltaforge/reference.py:558-568)
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+          const float gv = gate_v[g];
+          p.out[(long)b * p.out_stride + (long)(hq0 + g) * D + t] = f2bf(p.gate_swish ? silu_f(gv) : sigmoid_f(gv));
+        }
+      }
       if (t == 0) trace_mark(p.trace, cta, 6);
       return;
     }

@@ -356,10 +356,9 @@ struct Engine {
         cur_merge.ml = q.part_ml;
         cur_merge.nclusters = m.attn_splits / q.cluster_size;
         cur_merge.d = d_;
-        if (m.attn_output_gate) {
-          cur_merge.gate = proj + d_;
-          cur_merge.gateh_stride = 2L * d_;
-          cur_merge.gate_swish = m.gate_is_swish;
+        if (m.attn_output_gate) {  // the attention step leaves the activated gate where its output would have gone
+          cur_merge.gate = mix;
+          cur_merge.gateh_stride = d_;
         }
       }
       q.out = mix;

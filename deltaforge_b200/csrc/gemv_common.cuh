@@ -81,11 +81,8 @@ __device__ __forceinline__ void attn_merge_values(const AttnMerge& a, int k, flo
                        __uint_as_float(graw.y & 0xffff0000u)};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    float y = round_bf16(o[j] / l);
-    if (a.gate) {
-      const float gg = round_bf16(a.gate_swish ? silu_f(gl[j]) : sigmoid_f(gl[j]));
-      y = round_bf16(__fmul_rn(y, gg));
-    }
+    float y = round_bf16(__fdiv_rn(o[j], l));
+    if (a.gate) y = round_bf16(__fmul_rn(y, gl[j]));
     v[j] = y;
   }
 }

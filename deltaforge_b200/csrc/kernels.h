@@ -23,16 +23,16 @@ struct Trace {
 enum Prologue { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2, PRO_ATTN_MERGE = 3 };
 
 // The last step of split-KV attention, done by its consumer: head h's output is sum_c w_c acc[h][c][:] / sum_c w_c l[h][c]
-// with w_c = exp(m[h][c] - max_c m[h][c]), rounded to bf16, then multiplied by the bf16 output gate
-// (src/deltaforge/reference.py:558-568, :675-676). acc [heads, nclusters, d] fp32, ml [heads, nclusters, 2] = (m, l).
+// with w_c = exp(m[h][c] - max_c m[h][c]), rounded to bf16, then multiplied by the bf16 output gate, which the attention
+// step left already activated (src/deltaforge/reference.py:558-568, :675-676). acc [heads, nclusters, d] fp32,
+// ml [heads, nclusters, 2] = (m, l).
 struct AttnMerge {
   const float* acc;
   const float* ml;
   int nclusters;  // 1..8
   int d;          // head dim (a multiple of 128)
-  const bf16* gate;  // optional gate logits: element (h, i) at gate[h * gateh_stride + i]
+  const bf16* gate;  // optional activated gate, bf16(sigmoid(logit)): element (h, i) at gate[h * gateh_stride + i]
   long gateh_stride;
-  int gate_swish;
 };
 // EPI_PARTIAL_F32 (engine-internal, tensor parallelism): `out` is an fp32 buffer that receives the unrounded sum
 // EPI_PARTIAL_PEER (engine-internal): the unrounded sum goes, tagged with an epoch, straight into a slot of every
