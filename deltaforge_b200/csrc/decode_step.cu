@@ -221,6 +221,7 @@ struct Engine {
       p.conv_state = (bf16*)conv_layer->conv_state;
       p.conv_w = (const bf16*)conv_layer->conv_w;
       p.conv_dim = 2 * m.lin_k_heads * m.lin_dk + m.lin_v_heads * m.lin_dv;
+      p.conv_state_settled = 1;  // written by this projection of the previous token, a whole graph launch ago
     }
     p.partials = (float*)at(ws.partials);
     p.counters = (unsigned*)at(ws.counters);

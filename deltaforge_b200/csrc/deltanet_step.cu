@@ -149,11 +149,8 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   // 3. Recurrence; the updated slab goes straight back.
   const float o = delta_core(s, dk, col_ok, qn, kn, vval, gates[1], gates[0], red);
   if (t == 0) trace_mark(p.trace, cta, 3);
-#pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int k = warp * RPT + i;
-    if (col_ok && k < dk) __stcs(S + (long)k * dv + col, s[i]);
-  }
+  // (the updated slab is stored after the cluster exchange below: the barrier's release would otherwise wait for
+  // these 2 MB of stores to be acknowledged before the head's sum of squares could be read)
 
   // 4. Gated RMSNorm over the head's dv outputs: the CTAs of the cluster swap their sums of squares.
   const float ob = col_ok ? round_bf16(o) : 0.f;
@@ -166,6 +163,11 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   const float sz = silu_f(zval);  // needs nothing from the other CTAs: evaluated while their sums arrive
   cluster.sync();
   if (t == 0) trace_mark(p.trace, cta, 5);
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int k = warp * RPT + i;
+    if (col_ok && k < dk) __stcs(S + (long)k * dv + col, s[i]);
+  }
   float tot = 0.f;
   for (int rk = 0; rk < nvb; ++rk) tot += cluster_ss[rk];
   if (warp == 0 && col_ok) {

@@ -131,7 +131,7 @@ struct ClusterArgs {
 constexpr int MAX_TPC = 4;
 
 // TNW: columns per tile. CW: consumer warps (8 or 16); one more warp issues the copies.
-template <int TNW, int CW, bool NS>  // NS: odd rows' nibbles are used unshifted (16 x their value) in accumulators of their own
+template <int TNW, int CW>
 __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid_constant__ CUtensorMap wmap,
                                                                     const __grid_constant__ CUtensorMap smap, const ClusterArgs a) {
   constexpr int CT = CW * 32;          // consumer threads
@@ -307,9 +307,8 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
         if (ok) {
           if (!DFB_IN_BOUNDS(st < a.stages && s < a.max_units && i < a.tpc, a.status, 5)) break;
           const unsigned char* wbase = ring + (size_t)st * STAGE;
-          // even rows of a word sit in the low nibbles of its bytes, odd rows in the high nibbles: the odd rows are
-          // used where they are (16 x their value) in accumulators of their own, and shifted once per group
-          int acc_eh[4] = {0, 0, 0, 0}, acc_el[4] = {0, 0, 0, 0}, acc_oh[4] = {0, 0, 0, 0}, acc_ol[4] = {0, 0, 0, 0};
+          // even rows of a word sit in the low nibbles of its bytes, odd rows in the high nibbles
+          int acc_eh[4] = {0, 0, 0, 0}, acc_el[4] = {0, 0, 0, 0};
           int msum = 0;
 #pragma unroll
           for (int r = 0; r < RPT; ++r) {
@@ -321,19 +320,11 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint32_t ne = wv[q] & 0x0F0F0F0Fu;
-              if (NS) {
-                const uint32_t no = wv[q] & 0xF0F0F0F0u;
-                acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
-                acc_oh[q] = dp4a_us(no, xw.y, acc_oh[q]);
-                acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
-                acc_ol[q] = dp4a_uu(no, xw.w, acc_ol[q]);
-              } else {
-                const uint32_t no = (wv[q] >> 4) & 0x0F0F0F0Fu;
-                acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
-                acc_eh[q] = dp4a_us(no, xw.y, acc_eh[q]);
-                acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
-                acc_el[q] = dp4a_uu(no, xw.w, acc_el[q]);
-              }
+              const uint32_t no = (wv[q] >> 4) & 0x0F0F0F0Fu;
+              acc_eh[q] = dp4a_us(ne, xw.x, acc_eh[q]);
+              acc_eh[q] = dp4a_us(no, xw.y, acc_eh[q]);
+              acc_el[q] = dp4a_uu(ne, xw.z, acc_el[q]);
+              acc_el[q] = dp4a_uu(no, xw.w, acc_el[q]);
             }
           }
           float sc[4];
@@ -348,9 +339,7 @@ __global__ void __launch_bounds__(CW * 32 + 32) gemv_cluster_kernel(const __grid
           const float f = fg[s];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            // sum over this thread's rows of (nibble - 8) * m, exact: the odd-row part is a multiple of 16
-            const int S = NS ? (acc_eh[q] * 256 + acc_el[q]) + ((acc_oh[q] * 256 + acc_ol[q]) >> 4) - 8 * msum
-                             : acc_eh[q] * 256 + acc_el[q] - 8 * msum;
+            const int S = acc_eh[q] * 256 + acc_el[q] - 8 * msum;  // sum over this thread's rows of (nibble - 8) * m, exact
             tot[q] = fmaf((float)S * f, sc[q], tot[q]);
           }
           if (a.stages < total) {  // the stage goes back to the producer (only when units outnumber stages)
@@ -448,10 +437,14 @@ struct ClusterPlan {
   size_t smem;
 };
 
-int env_int(const char* name, int fallback) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : fallback;
-}
+// Measured on the full-size decode step: sixteen consumer warps cost the second resident CTA per SM (registers) and
+// ran a third slower; grids above one and a half CTAs per SM are folded; a ring of about 125 KB (seven 256-column
+// stages) was the fastest depth for the folded grids.
+constexpr int CONSUMER_WARPS = 8;
+constexpr int FOLD_ABOVE_CTAS = 222;
+constexpr int RING_BYTES = 125 << 10;
+constexpr int MIN_STAGES = 5;
+constexpr int SWIGLU_CLUSTER = 2;
 
 template <int TNW>
 ClusterPlan plan_cluster(int K, int N, bool swiglu) {
@@ -462,26 +455,26 @@ ClusterPlan plan_cluster(int K, int N, bool swiglu) {
   if (swiglu) {
     // a tile pairs TNW/2 gate columns with their up columns; small clusters place well (the CTAs of a cluster must sit
     // in one GPC, and GPCs of 18 or 20 SMs hold only 34 clusters of four single-CTA-per-SM blocks but 74 of two)
-    c.cs = std::min(c.cs, env_int("DFB_SWIGLU_CS", 2));
+    c.cs = std::min(c.cs, SWIGLU_CLUSTER);
     c.tiles = (N / 2 + TNW / 2 - 1) / (TNW / 2);
   }
   c.max_units = (G + c.cs - 1) / c.cs;
-  c.cw = env_int("DFB_CW", 8);
+  c.cw = CONSUMER_WARPS;
   const int sms = 148;
   const int ctas = c.tiles * c.cs;
-  c.tpc = ctas > env_int("DFB_FOLD_ABOVE", 222) ? std::min(MAX_TPC, (ctas + sms - 1) / sms) : 1;
+  c.tpc = ctas > FOLD_ABOVE_CTAS ? std::min(MAX_TPC, (ctas + sms - 1) / sms) : 1;
   c.clusters = (c.tiles + c.tpc - 1) / c.tpc;
   const size_t stage = (size_t)UROWS * TNW * 4 + TNW * 4;
   // everything resident when it fits in about 100 KB (two CTAs per SM); a ring of stages the consumers recycle otherwise
-  const int ring_cap = (int)(((size_t)env_int("DFB_RING_KB", 125) << 10) / stage);
-  c.stages = std::min(c.tpc * c.max_units, std::max(env_int("DFB_MIN_STAGES", 5), ring_cap));
+  const int ring_cap = (int)((size_t)RING_BYTES / stage);
+  c.stages = std::min(c.tpc * c.max_units, std::max(MIN_STAGES, ring_cap));
   const int rl = c.cw * 32 / (TNW / 4);
   c.smem = (size_t)c.stages * stage + (size_t)c.max_units * UROWS * 16 + (size_t)c.max_units * UROWS * 4 +
            (size_t)((c.max_units + 3) & ~3) * 4 + (size_t)rl * TNW * 4 + (size_t)c.tpc * c.cs * TNW * 4 + (size_t)c.stages * 16 + 64 + 128;
   return c;
 }
 
-template <int TNW, int CW, bool NS>
+template <int TNW, int CW>
 int launch_cluster_cfg(const GemvParams& p, const ClusterPlan& c, const CUtensorMap& wmap, const CUtensorMap& smap, int* status,
                        cudaStream_t stream) {
   ClusterArgs a = {};
@@ -506,7 +499,7 @@ int launch_cluster_cfg(const GemvParams& p, const ClusterPlan& c, const CUtensor
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW, CW, NS>, wmap, smap, a);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_cluster_kernel<TNW, CW>, wmap, smap, a);
   if (e != cudaSuccess) {
     set_error("int4 gemv (cluster): launch failed: %s", cudaGetErrorString(e));
     return 1;
@@ -550,9 +543,7 @@ int launch_cluster_tnw(const GemvParams& p, int* status, cudaStream_t stream) {
     }
   }
   const ClusterPlan c = plan_cluster<TNW>(p.K, p.N, p.epilogue == EPI_SWIGLU);
-  if (c.cw == 8 && env_int("DFB_NOSHIFT", 0)) return launch_cluster_cfg<TNW, 8, true>(p, c, wmap, smap, status, stream);
-  if (c.cw == 8) return launch_cluster_cfg<TNW, 8, false>(p, c, wmap, smap, status, stream);
-  return launch_cluster_cfg<TNW, 16, true>(p, c, wmap, smap, status, stream);
+  return launch_cluster_cfg<TNW, CONSUMER_WARPS>(p, c, wmap, smap, status, stream);
 }
 
 }  // namespace
@@ -581,12 +572,8 @@ int cluster_configure() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e == cudaSuccess) e = prefer_max_shared(kernel);
   };
-  opt_in(gemv_cluster_kernel<256, 8, false>);
-  opt_in(gemv_cluster_kernel<256, 8, true>);
-  opt_in(gemv_cluster_kernel<256, 16, true>);
-  opt_in(gemv_cluster_kernel<128, 8, false>);
-  opt_in(gemv_cluster_kernel<128, 8, true>);
-  opt_in(gemv_cluster_kernel<128, 16, true>);
+  opt_in(gemv_cluster_kernel<256, CONSUMER_WARPS>);
+  opt_in(gemv_cluster_kernel<128, CONSUMER_WARPS>);
   if (e != cudaSuccess) return check_launch("int4 gemv (cluster): shared-memory opt-in");
   return 0;
 }

@@ -19,10 +19,17 @@
 //    so column j of the product is piece j of 16 * sum nibble * m.
 //    In "pair" mode (gate_proj|up_proj) a tile is 128 gate columns followed by the 128 up columns of the same
 //    channels, so the CTA that finishes a tile can apply SwiGLU.
-//  * Work split, data movement, reduction, prologues and epilogues are those of int4_gemv_cluster.cu: a cluster of
-//    CTAs per tile splits the groups, every CTA fills its ring of units before griddepcontrol.wait, column sums
-//    go to the cluster's first CTA through distributed shared memory, one cluster barrier, fixed-order sums.
-//    A column is owned by one lane here, so there is no row-lane reduction inside the CTA.
+//  * Data movement, prologues and epilogues are those of int4_gemv_cluster.cu: a cluster of CTAs per tile splits the
+//    groups, every CTA fills its ring of units before griddepcontrol.wait, column sums go to the cluster's first CTA
+//    through distributed shared memory, one cluster barrier, fixed-order sums.
+//  * Work split inside a CTA: the tile is cut into chunks of four 16-column blocks; a warp owns one chunk and every
+//    second (256-column tiles) or fourth (128-column tiles) unit of it. The four blocks of a unit are four independent
+//    chains of mma, so a warp is not waiting on one chain of dependent instructions per unit (a warp that owned two
+//    blocks and walked through every unit spent 800 cycles per unit, nearly all of it latency). The warps of a chunk
+//    add their column sums through shared memory in warp order. Every unit has an mbarrier of its own (used once), so a
+//    warp that reads only some units never meets a barrier phase it skipped.
+//  * Measured on B200 for this instruction: one mma.sync.m16n8k32 (u8 x s8) per 8.1 cycles per SM sub-core, 21 cycles
+//    of latency; the u4 x s4 form (m16n8k64) is emulated at about 220 cycles and is not used.
 //
 // Every mbarrier wait is bounded (about two seconds); a CTA whose wait gives up records a code in the status word
 // and still takes part in the cluster barrier.
@@ -121,9 +128,56 @@ __device__ __forceinline__ int tile_column(int tile, int col, int N, int pair) {
   return n < N ? n : -1;
 }
 
-template <int TN>  // columns per tile: 256 (two 16-column blocks per warp) or 128 (one)
+// One group (local index gl) by one warp: v[i] is row 4 * lane + i. Writes the group's exponent factor, integer sum and
+// B-fragment bytes. (Two groups at a time per warp, their shuffle chains interleaved, measured slower.)
+__device__ __forceinline__ void quantise_group(const float (&v)[4], int gl, float* fg, int* msum, unsigned char* xb, int lane) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = warp_max(amax);
+  int E = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
+  E = max(E, -100);
+  const float up = __uint_as_float((uint32_t)(127 + 13 - E) << 23);  // 2^(13-E): |x| * up < 2^14
+  if (lane == 0) fg[gl] = __uint_as_float((uint32_t)(127 - 13 + E - 4) << 23);  // 2^(E-13) / 16
+  int ms = 0;
+  uint32_t e0 = 0, e1 = 0, e2 = 0, o0 = 0, o1 = 0;  // this lane's halves (16 bits: two rows each) of the five B words
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = __float2int_rn(v[i] * up);
+    ms += m;
+    const int sh = (i >> 1) * 8;  // rows 4l+0, 4l+1 -> byte 0 of the half; rows 4l+2, 4l+3 -> byte 1
+    if ((i & 1) == 0) {  // even row: the three signed byte-pieces of 16 m
+      const int q = m * 16;
+      const int p0 = (int)(signed char)(q & 0xff);
+      const int r1 = (q - p0) >> 8;
+      const int p1 = (int)(signed char)(r1 & 0xff);
+      const int p2 = (r1 - p1) >> 8;
+      e0 |= (uint32_t)(p0 & 0xff) << sh, e1 |= (uint32_t)(p1 & 0xff) << sh, e2 |= (uint32_t)(p2 & 0xff) << sh;
+    } else {  // odd row: the two signed byte-pieces of m
+      const int l0 = (int)(signed char)(m & 0xff);
+      const int h0 = (m - l0) >> 8;
+      o0 |= (uint32_t)(l0 & 0xff) << sh, o1 |= (uint32_t)(h0 & 0xff) << sh;
+    }
+  }
+  ms = (int)__reduce_add_sync(0xffffffffu, ms);
+  if (lane == 0) msum[gl] = ms;
+  // lanes 2r (rows 0..3 of word row r: bytes 0, 1) and 2r+1 (rows 4..7: bytes 2, 3) complete each other's words
+  const int hs = (lane & 1) * 16;
+  e0 <<= hs, e1 <<= hs, e2 <<= hs, o0 <<= hs, o1 <<= hs;
+  e0 |= __shfl_xor_sync(0xffffffffu, e0, 1), e1 |= __shfl_xor_sync(0xffffffffu, e1, 1), e2 |= __shfl_xor_sync(0xffffffffu, e2, 1);
+  o0 |= __shfl_xor_sync(0xffffffffu, o0, 1), o1 |= __shfl_xor_sync(0xffffffffu, o1, 1);
+  // B column c of word row kb: (b0, b1) at xb[group][kb][c]; columns 3..7 are zero
+  uint2* row = (uint2*)(xb + (size_t)gl * XB_BYTES) + (lane >> 1) * 8;
+  if ((lane & 1) == 0) {
+    row[0] = make_uint2(e0, o0), row[1] = make_uint2(e1, o1), row[2] = make_uint2(e2, 0u), row[3] = make_uint2(0u, 0u);
+  } else {
+    row[4] = row[5] = row[6] = row[7] = make_uint2(0u, 0u);
+  }
+}
+
+template <int TN>  // TN columns per tile: 256 (two 16-column blocks per warp) or 128 (one)
 __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
-  constexpr int NB = TN / 128;             // 16-column blocks per warp
+  constexpr int CH = TN / 64;              // chunks of four 16-column blocks per tile
   constexpr int W_BYTES = TN / 16 * 1024;  // bytes of words per unit
   extern __shared__ unsigned char smem_raw[];
   const GemvParams& p = a.p;
@@ -134,9 +188,11 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
   float* fg = (float*)(msum + ((a.max_units + 3) & ~3));           // [max_units] 2^e / 16 per group
   float* dsm = fg + ((a.max_units + 3) & ~3);                      // [cs][TN] column sums from every rank (used in rank 0)
   float* red = dsm + a.cs * TN;                                    // [TN] scratch of the SwiGLU epilogue
-  uint64_t* full = (uint64_t*)(red + TN);                          // [stages]
-  uint64_t* empty = full + a.stages;                               // [stages]
+  uint64_t* full = (uint64_t*)(red + TN);                          // [max_units] one per unit, each used once: a warp that
+                                                                   // reads only some units never meets a phase it skipped
+  uint64_t* empty = full + a.max_units;                            // [stages]
   float* wred = (float*)(empty + a.stages);                        // [16]
+  float* part = wred + 16;                                         // [CW][64] column sums of every warp's units
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const int cs = a.cs;
@@ -149,10 +205,8 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
 
   if (t == 0) {
     trace_mark(p.trace, cta, 0);
-    for (int s = 0; s < a.stages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], CW);
-    }
+    for (int s = 0; s < a.max_units; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < a.stages; ++s) mbar_init(&empty[s], CH);  // one arrival per chunk = per warp that reads the unit
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -172,33 +226,48 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
           atomicExch(a.status, 6);
           break;
         }
-        mbar_expect_tx(&full[st], (uint32_t)a.unit_bytes);
-        bulk_load(ring + (size_t)st * a.unit_bytes, src + (size_t)j * a.unit_bytes, (uint32_t)a.unit_bytes, &full[st], pol);
+        mbar_expect_tx(&full[j], (uint32_t)a.unit_bytes);
+        bulk_load(ring + (size_t)st * a.unit_bytes, src + (size_t)j * a.unit_bytes, (uint32_t)a.unit_bytes, &full[j], pol);
         if (++st == a.stages) st = 0, ++round;
         if (j + 1 == min(nunits, a.stages)) trace_mark(p.trace, cta, 7);
       }
     }
     __syncwarp();  // the whole warp takes part in the (aligned) cluster barrier below
   } else {
+    // What this CTA reads that no kernel of this token writes goes in flight before the wait for the previous kernel: the
+    // norm weights of the groups it quantises, and, where the caller says the history was last written before this stream's
+    // current work began (the decode engine: one token ago), the conv taps and history its epilogue uses.
+    uint2 xraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)}, wraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+    const int my_n = t < TN ? tile_column<TN>(tile, t, p.N, 0) : -1;
+    const bool finisher = (cs == 1 || rank == 0) && !swiglu && my_n >= 0;
+    if (p.prologue == PRO_RMSNORM) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (warp + j * CW < nunits) wraw[j] = *(const uint2*)(p.norm_w + (g0 + warp + j * CW) * 128 + lane * 4);
+    }
+    const float inv_k = __frcp_rn((float)p.K);
+    const bool conv_early = p.epilogue == EPI_CONV && p.conv_state_settled;
+    if (finisher && conv_early) pre = epilogue_preload(p, 0, my_n);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
     if (t == 0) trace_mark(p.trace, cta, 1);
     // Everything this CTA reads that an earlier kernel wrote goes in flight at once.
     // (the first two groups each warp quantises: a CTA holds at most sixteen groups in practice, so this is all of them)
-    uint2 xraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)}, wraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
 #pragma unroll
     for (int j = 0; j < 2; ++j)
       if (warp + j * CW < nunits && p.prologue != PRO_ATTN_MERGE) {
         const int k = (g0 + warp + j * CW) * 128 + lane * 4;
         xraw[j] = *(const uint2*)(p.x + k);
-        if (p.prologue == PRO_RMSNORM) wraw[j] = *(const uint2*)(p.norm_w + k);
         if (p.prologue == PRO_SILU_MUL) wraw[j] = *(const uint2*)(p.up + k);
       }
-    const int my_n = t < TN ? tile_column<TN>(tile, t, p.N, 0) : -1;
-    if ((cs == 1 || rank == 0) && !swiglu && my_n >= 0) pre = epilogue_preload(p, 0, my_n);
+    if (finisher && !conv_early) pre = epilogue_preload(p, 0, my_n);
     float rstd = 1.f;
     if (p.prologue == PRO_RMSNORM) {
       float tot = 0.f;
-      if (p.ss_in) {  // the kernel that wrote x left the sums of squares of its tiles
+      if (p.ss_in && p.ss_count <= 32) {
+        // the kernel that wrote x left the sums of squares of its tiles: one load per lane and a shuffle tree (the same
+        // tree in every warp of every CTA, so all of them get the same bits), not a chain of dependent loads
+        tot = warp_sum(lane < p.ss_count ? p.ss_in[lane] : 0.f);
+      } else if (p.ss_in) {
         for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
       } else {
         float ss = 0.f;
@@ -212,23 +281,26 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
 #pragma unroll
         for (int w = 0; w < CW; ++w) tot += wred[w];
       }
-      rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps));
+      // 1 / sqrt(mean + eps) by the reciprocal-square-root unit and one Newton step (within an ulp of the two correctly
+      // rounded steps the slower kernels take; the chain of dependent instructions is a third as long)
+      const float y = fmaf(tot, inv_k, p.eps);
+      const float r = rsqrtf(y);
+      rstd = r * fmaf(-0.5f * y * r, r, 1.5f);
     }
-    // One warp per group of this CTA: shared exponent, 15-bit integers m (|m| < 2^14), cut into signed bytes in the
-    // order the mma's B fragments are read. Lane l holds rows 4l .. 4l+3 of the group = half of word row l/2.
+    // One warp per group of this CTA: shared exponent, 15-bit integers m (|m| < 2^14), cut into signed bytes in the order
+    // the mma's B fragments are read. Lane l holds rows 4l .. 4l+3 of the group = half of word row l/2.
     for (int gl = warp; gl < nunits; gl += CW) {
-      const int g = g0 + gl;
       float v[4];
-      uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
-      if (gl >= warp + 2 * CW && p.prologue != PRO_ATTN_MERGE) {  // a third group and later: loaded here
-        const int k = g * 128 + lane * 4;
-        xv = *(const uint2*)(p.x + k);
-        if (p.prologue == PRO_RMSNORM) wv = *(const uint2*)(p.norm_w + k);
-        if (p.prologue == PRO_SILU_MUL) wv = *(const uint2*)(p.up + k);
-      }
       if (p.prologue == PRO_ATTN_MERGE) {
-        attn_merge_values(p.merge, g * 128 + lane * 4, v);
+        attn_merge_values(p.merge, (g0 + gl) * 128 + lane * 4, v);
       } else {
+        uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
+        if (gl >= warp + 2 * CW) {  // a third group and later: loaded here
+          const int k = (g0 + gl) * 128 + lane * 4;
+          xv = *(const uint2*)(p.x + k);
+          if (p.prologue == PRO_RMSNORM) wv = *(const uint2*)(p.norm_w + k);
+          if (p.prologue == PRO_SILU_MUL) wv = *(const uint2*)(p.up + k);
+        }
         const float xr[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16),
                              __uint_as_float(xv.y & 0xffff0000u)};
         const float wr[4] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
@@ -236,135 +308,88 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
       }
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = warp_max(amax);
-      int E = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
-      E = max(E, -100);
-      const float up = __uint_as_float((uint32_t)(127 + 13 - E) << 23);  // 2^(13-E): |x| * up < 2^14
-      if (lane == 0) fg[gl] = __uint_as_float((uint32_t)(127 - 13 + E - 4) << 23);  // 2^(E-13) / 16
-      int ms = 0;
-      // this lane's halves (16 bits: two rows each) of the five B words of its word row
-      uint32_t e0 = 0, e1 = 0, e2 = 0, o0 = 0, o1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int m = __float2int_rn(v[i] * up);
-        ms += m;
-        const int sh = (i >> 1) * 8;  // rows 4l+0, 4l+1 -> byte 0 of the half; rows 4l+2, 4l+3 -> byte 1
-        if ((i & 1) == 0) {  // even row: the three signed byte-pieces of 16 m
-          const int q = m * 16;
-          const int p0 = (int)(signed char)(q & 0xff);
-          const int r1 = (q - p0) >> 8;
-          const int p1 = (int)(signed char)(r1 & 0xff);
-          const int p2 = (r1 - p1) >> 8;
-          e0 |= (uint32_t)(p0 & 0xff) << sh, e1 |= (uint32_t)(p1 & 0xff) << sh, e2 |= (uint32_t)(p2 & 0xff) << sh;
-        } else {  // odd row: the two signed byte-pieces of m
-          const int l0 = (int)(signed char)(m & 0xff);
-          const int h0 = (m - l0) >> 8;
-          o0 |= (uint32_t)(l0 & 0xff) << sh, o1 |= (uint32_t)(h0 & 0xff) << sh;
-        }
-      }
-      ms = (int)__reduce_add_sync(0xffffffffu, ms);
-      if (lane == 0) msum[gl] = ms;
-      // lanes 2j (rows 0..3 of word row j: bytes 0, 1) and 2j+1 (rows 4..7: bytes 2, 3) complete each other's words
-      const int hs = (lane & 1) * 16;
-      e0 <<= hs, e1 <<= hs, e2 <<= hs, o0 <<= hs, o1 <<= hs;
-      e0 |= __shfl_xor_sync(0xffffffffu, e0, 1), e1 |= __shfl_xor_sync(0xffffffffu, e1, 1), e2 |= __shfl_xor_sync(0xffffffffu, e2, 1);
-      o0 |= __shfl_xor_sync(0xffffffffu, o0, 1), o1 |= __shfl_xor_sync(0xffffffffu, o1, 1);
-      // B column j of word row kb: (b0, b1) at xb[gl][kb][j]; columns 3..7 are zero
-      uint2* row = (uint2*)(xb + (size_t)gl * XB_BYTES) + (lane >> 1) * 8;
-      if ((lane & 1) == 0) {
-        row[0] = make_uint2(e0, o0), row[1] = make_uint2(e1, o1), row[2] = make_uint2(e2, 0u), row[3] = make_uint2(0u, 0u);
-      } else {
-        row[4] = row[5] = row[6] = row[7] = make_uint2(0u, 0u);
-      }
+      quantise_group(v, gl, fg, msum, xb, lane);
     }
     consumer_sync();
     if (t == 0) trace_mark(p.trace, cta, 2);
 
-    // warp w owns the 16-column blocks 2w and 2w+1 of the tile; lane = 4 * gq + tq: rows gq and gq + 8 of the mma,
-    // word row tq of every 32-row step
+    // The tile is cut into chunks of four 16-column blocks. A warp owns one chunk (warp % CH) and every (CW / CH)-th
+    // unit of it, so the four blocks of a unit give it four independent chains of mma and a unit is waited for once per
+    // chunk. lane = 4 * gq + tq: rows gq and gq + 8 of the mma, word row tq of every 32-row step.
     const int gq = lane >> 2, tq = lane & 3;
     const int mul0 = tq == 0 ? 1 : (tq == 1 ? 65536 : 0), mul1 = tq == 0 ? 256 : 0;
-    float tot[NB][2] = {};
-    // With every unit of this CTA resident (nothing is recycled) all arrivals are awaited first: no barrier instruction
-    // then sits between the units, and one unit's loads overlap the arithmetic of the unit before.
-    const bool resident = a.stages >= nunits;
-    if (resident)
-      for (int s = 0; s < nunits; ++s)
-        if (ok) ok = mbar_wait(&full[s], 0);
-    int st = 0, phase = 0;
-    for (int s = 0; s < nunits; ++s) {
-      if (!resident && ok) ok = mbar_wait(&full[st], phase);
-      if (ok) {
-        if (!DFB_IN_BOUNDS(st < a.stages && s < a.max_units, a.status, 2)) break;
-        const unsigned char* ub = ring + (size_t)st * a.unit_bytes;
-        const uint2* xrow = (const uint2*)(xb + (size_t)s * XB_BYTES);
-        // everything the unit needs from shared memory goes in flight at once; the two halves of the group's rows get
-        // accumulators of their own, so that only two mma depend on one another
-        uint4 w[2][NB];
-        uint2 bv[4];
+    const int ch = warp % CH;
+    float tot[4][2] = {};
+    int st = warp / CH;  // = s mod stages: the first units fit the ring (stages >= CW / CH whenever units outnumber stages)
+    for (int s = warp / CH; s < nunits; s += CW / CH, st += CW / CH) {
+      while (st >= a.stages) st -= a.stages;
+      if (ok) ok = mbar_wait(&full[s], 0);
+      if (!ok || !DFB_IN_BOUNDS(st < a.stages && s < a.max_units, a.status, 2)) break;
+      const unsigned char* ub = ring + (size_t)st * a.unit_bytes;
+      const uint2* xrow = (const uint2*)(xb + (size_t)s * XB_BYTES);
+      uint2 bv[4];
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr)
+      for (int ks = 0; ks < 4; ++ks) bv[ks] = xrow[(ks * 4 + tq) * 8 + gq];
+      int c[4][4];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) w[pr][b] = *(const uint4*)(ub + (size_t)(NB * warp + b) * 1024 + (pr * 32 + lane) * 16);
+      for (int b = 0; b < 4; ++b) c[b][0] = c[b][1] = c[b][2] = c[b][3] = 0;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) bv[ks] = xrow[(ks * 4 + tq) * 8 + gq];
-        int ch[2][NB][4] = {};
+      for (int pr = 0; pr < 2; ++pr) {
+        uint4 w[4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int b = 0; b < 4; ++b) w[b] = *(const uint4*)(ub + (size_t)(4 * ch + b) * 1024 + (pr * 32 + lane) * 16);
 #pragma unroll
-          for (int pr = 0; pr < 2; ++pr)
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-              const uint32_t wa = h ? w[pr][b].z : w[pr][b].x, wb = h ? w[pr][b].w : w[pr][b].y;  // columns gq and gq + 8
-              imma(ch[pr][b], wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, wa & 0xF0F0F0F0u, wb & 0xF0F0F0F0u, bv[2 * pr + h].x, bv[2 * pr + h].y);
-            }
-        int c[NB][4];
-#pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) c[b][i] = ch[0][b][i] + ch[1][b][i];
-        const float f = fg[s];
-        const int zp = tq == 0 ? 128 * msum[s] : 0;  // the zero point: 16 * 8 * sum m, taken off where piece 0 lives
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          // scales of columns gq and gq + 8 of this block, stored as the pair this lane reads
-          float s0, s1;
-          const unsigned char* sp = ub + W_BYTES;
-          if (p.scale_bf16) {
-            const uint32_t v = *(const uint32_t*)(sp + ((NB * warp + b) * 8 + gq) * 4);
-            s0 = __uint_as_float(v << 16), s1 = __uint_as_float(v & 0xffff0000u);
-          } else {
-            const float2 v = *(const float2*)(sp + ((NB * warp + b) * 8 + gq) * 8);
-            s0 = v.x, s1 = v.y;
+          for (int b = 0; b < 4; ++b) {
+            const uint32_t wa = h ? w[b].z : w[b].x, wb = h ? w[b].w : w[b].y;  // columns gq and gq + 8
+            imma(c[b], wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, wa & 0xF0F0F0F0u, wb & 0xF0F0F0F0u, bv[2 * pr + h].x, bv[2 * pr + h].y);
           }
-          const int i0 = c[b][0] * mul0 + c[b][1] * mul1 - zp, i1 = c[b][2] * mul0 + c[b][3] * mul1 - zp;
-          tot[b][0] = fmaf((float)i0 * f, s0, tot[b][0]);
-          tot[b][1] = fmaf((float)i1 * f, s1, tot[b][1]);
-        }
-        if (a.stages < nunits) {  // the stage goes back to the producer (only when units outnumber stages)
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty[st]);
         }
       }
-      if (s == 0 && t == 0) trace_mark(p.trace, cta, 4);  // the first unit is done: what follows is the steady state
-      if (++st == a.stages) st = 0, phase ^= 1;
+      const float f = fg[s];
+      const int zp = tq == 0 ? 128 * msum[s] : 0;  // the zero point: 16 * 8 * sum m, taken off where piece 0 lives
+      const unsigned char* sp = ub + W_BYTES;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        // scales of columns gq and gq + 8 of this block, stored as the pair this lane reads
+        float s0, s1;
+        if (p.scale_bf16) {
+          const uint32_t v = *(const uint32_t*)(sp + ((4 * ch + b) * 8 + gq) * 4);
+          s0 = __uint_as_float(v << 16), s1 = __uint_as_float(v & 0xffff0000u);
+        } else {
+          const float2 v = *(const float2*)(sp + ((4 * ch + b) * 8 + gq) * 8);
+          s0 = v.x, s1 = v.y;
+        }
+        const int i0 = c[b][0] * mul0 + c[b][1] * mul1 - zp, i1 = c[b][2] * mul0 + c[b][3] * mul1 - zp;
+        tot[b][0] = fmaf((float)i0 * f, s0, tot[b][0]);
+        tot[b][1] = fmaf((float)i1 * f, s1, tot[b][1]);
+      }
+      if (a.stages < nunits) {  // the stage goes back to the producer (only when units outnumber stages)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+      }
+      if (s == 0 && t == 0) trace_mark(p.trace, cta, 4);  // the first unit is done
     }
     if (!ok && lane == 0) atomicExch(a.status, 4);
     if (t == 0) trace_mark(p.trace, cta, 3);
-    // pieces 0, 1 sit in lane tq = 0, piece 2 in lane tq = 1: one exchange, then lane tq = 0 owns the column sums
+    // pieces 0, 1 sit in lane tq = 0, piece 2 in lane tq = 1: one exchange, then lane tq = 0 owns the column sums of this
+    // warp's units; the warps of a chunk are added in warp order, and the CTA's column sums go to the cluster's first CTA
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < 4; ++b) {
       tot[b][0] += __shfl_xor_sync(0xffffffffu, tot[b][0], 1);
       tot[b][1] += __shfl_xor_sync(0xffffffffu, tot[b][1], 1);
       if (tq == 0) {
-        const int col = (NB * warp + b) * 16 + gq;
-        if (!DFB_IN_BOUNDS(rank < cs && col + 8 < TN, a.status, 3)) continue;
-        dsmem_store(dsm + rank * TN + col, 0, tot[b][0]);
-        dsmem_store(dsm + rank * TN + col + 8, 0, tot[b][1]);
+        part[warp * 64 + b * 16 + gq] = tot[b][0];
+        part[warp * 64 + b * 16 + gq + 8] = tot[b][1];
       }
+    }
+    consumer_sync();
+    if (t < TN && DFB_IN_BOUNDS(rank < cs, a.status, 3)) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = t / 64; w < CW; w += CH) v += part[w * 64 + (t & 63)];
+      dsmem_store(dsm + rank * TN + t, 0, v);
     }
   }
   if (cs > 1) cluster_barrier();  // every thread of every CTA of the cluster, the producer warps included
@@ -471,7 +496,7 @@ MmaPlan plan_mma(int K, int N, int pair, int scale_bf16) {
   c.unit_bytes = mma_unit_bytes(c.tn, scale_bf16);
   c.stages = std::min(c.max_units, std::max(4, (int)(((size_t)125 << 10) / c.unit_bytes)));
   c.smem = (size_t)c.stages * c.unit_bytes + (size_t)c.max_units * XB_BYTES + (size_t)((c.max_units + 3) & ~3) * 8 +
-           (size_t)c.cs * c.tn * 4 + (size_t)c.tn * 4 + (size_t)c.stages * 16 + 64 + 128;
+           (size_t)c.cs * c.tn * 4 + (size_t)c.tn * 4 + (size_t)(c.max_units + c.stages) * 8 + 64 + (size_t)CW * 64 * 4 + 128;
   return c;
 }
 
@@ -512,10 +537,13 @@ bool mma_path_ok(const GemvParams& p) {
 }
 
 int mma_configure() {
-  cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  if (e == cudaSuccess) e = prefer_max_shared(gemv_mma_kernel<256>);
-  if (e == cudaSuccess) e = prefer_max_shared(gemv_mma_kernel<128>);
+  cudaError_t e = cudaSuccess;
+  auto opt_in = [&e](auto kernel) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess) e = prefer_max_shared(kernel);
+  };
+  opt_in(gemv_mma_kernel<256>);
+  opt_in(gemv_mma_kernel<128>);
   if (e != cudaSuccess) return check_launch("int4 gemv (mma): shared-memory opt-in");
   return 0;
 }

@@ -85,6 +85,7 @@ struct GemvParams {
   bf16* conv_state;  // EPI_CONV: columns < conv_dim go through the 4-tap conv + SiLU, [rows, conv_dim, 3]
   const bf16* conv_w;  // [conv_dim, 4]
   int conv_dim;
+  int conv_state_settled;  // 1: no kernel still in flight on the stream writes conv_state (it may be read before the dependency wait)
   // scratch: split-K partial sums [rows, K/256, N] fp32 and one arrival counter per column tile
   float* partials;
   unsigned* counters;

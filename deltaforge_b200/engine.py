@@ -239,9 +239,10 @@ def default_attn_splits(max_seq_len: int, batch: int, kv_heads: int, sm_count: i
     while splits < 128 and -(-max_seq_len // splits) > 160:
         splits *= 2
     if batch <= 2 and -(-max_seq_len // splits) <= 160:
-        # shorter slices while the grid still fits the GPU in one go (a slice's staging buffer shrinks with it, so two or
-        # three CTAs share an SM): the scan of a slice is the long pole of the kernel
-        while splits * 2 <= 128 and splits * 2 * batch * kv_heads <= 2 * sm_count and max_seq_len // (splits * 2) >= 64:
+        # Short caches: still use the SMs. (More, shorter slices than one CTA per SM were measured at 4K tokens: 256 CTAs
+        # of 105 KB cannot sit beside the projection before them, start in waves only when it has left, and the kernel
+        # takes 20 us instead of 12.)
+        while splits * 2 * batch * kv_heads <= sm_count and max_seq_len // (splits * 2) >= 64:
             splits *= 2
         return splits
     # longer caches take the two-kernel path, which has no slice limit: about eight waves of CTAs, slices of

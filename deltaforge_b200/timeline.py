@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-MARKS = ("entry", "wait_ret", "x_ready", "dots_done", "cta_sum", "barrier", "exit", "issued")
+MARKS = ("entry", "wait_ret", "x_ready", "dots_done", "unit1_done", "barrier", "exit", "issued")
 
 
 def launch_names(layer_kinds: list[str], launches: int) -> list[str]:

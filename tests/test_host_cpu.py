@@ -113,7 +113,7 @@ def test_byte_model_matches_the_survey_arithmetic():
 
 
 def test_default_attention_slices():
-    assert engine.default_attn_splits(4240, 1, 4) == 64  # 67 keys per slice, 256 CTAs of 67 KB: one go on 148 SMs
+    assert engine.default_attn_splits(4240, 1, 4) == 32  # 133 keys per slice, 128 CTAs
     assert engine.default_attn_splits(8192, 1, 4) == 64
     assert engine.default_attn_splits(16, 2, 1) == 1
     s = engine.default_attn_splits(32768 + 64, 32, 4)
