@@ -487,14 +487,18 @@ MmaPlan plan_mma(int K, int N, int pair, int scale_bf16) {
   const int G = K / 128;
   c.tn = mma_tn(N, pair);
   c.tiles = mma_tiles(N, pair);
-  // The groups of a tile are split over a cluster so that the grid is at most about one and a half CTAs per SM (more
-  // would not be resident in one go). Clusters must be placed inside one GPC (18 or 20 SMs), so small ones place best:
-  // a gate|up pair (72 tiles) takes clusters of two.
-  c.cs = 1;
-  while (c.cs < MAX_CS && c.tiles * c.cs * 2 <= 222 && G / (c.cs * 2) >= 2) c.cs *= 2;
+  // The groups of a tile are split over a cluster of up to eight CTAs, as many as keep the grid within about 250 CTAs
+  // (one and two thirds per SM: with at most 84 KB of ring each, two fit on an SM beside the CTAs of the kernels before
+  // and after, which is what lets every kernel of the chain fetch its weights while its predecessor runs), then as few
+  // as give the same number of groups per CTA. Measured on the full-size decode step: gate|up (72 tiles) 3, the input
+  // projections (49 and 40 tiles of 20 groups) 5, the 2560-column projections (20 tiles) 8; each of 2, 4 and 6 in
+  // place of 3 and 5 was slower, as was a ring of 68, 100 or 125 KB in place of 84.
+  const int c_max = std::max(1, std::min({MAX_CS, 250 / std::max(1, c.tiles), G / 2}));
+  c.cs = c_max;
+  while (c.cs > 1 && (G + c.cs - 2) / (c.cs - 1) == (G + c_max - 1) / c_max) --c.cs;
   c.max_units = (G + c.cs - 1) / c.cs;
   c.unit_bytes = mma_unit_bytes(c.tn, scale_bf16);
-  c.stages = std::min(c.max_units, std::max(4, (int)(((size_t)125 << 10) / c.unit_bytes)));
+  c.stages = std::min(c.max_units, std::max(4, (int)(((size_t)84 << 10) / c.unit_bytes)));
   c.smem = (size_t)c.stages * c.unit_bytes + (size_t)c.max_units * XB_BYTES + (size_t)((c.max_units + 3) & ~3) * 8 +
            (size_t)c.cs * c.tn * 4 + (size_t)c.tn * 4 + (size_t)(c.max_units + c.stages) * 8 + 64 + (size_t)CW * 64 * 4 + 128;
   return c;
