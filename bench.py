@@ -45,8 +45,12 @@ WORKLOAD = "qwen3.5-4b int4 decode step, batch 1, ctx 4096: 32 layers [3 Gated D
 METRIC = "decode tokens/s (bs1, 4K ctx)"
 
 
-HEAD_GEMV_DRAM_BYTES_PER_LAUNCH = 327_891_968 + 4_020_096  # read + write, mean of two captured launches
-LAYER_GEMV_DRAM_BYTES_PER_LAUNCH = None  # average over the layer projections, from an ncu capture; None until one is taken
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of these kernels on these matrices (records of
+# those captures, not re-measured by a bench run). Head: mean of two captured launches. Layer projections: 24 DeltaNet
+# layers at 16.733 + 5.469 + 24.390 + 12.238 MB and 8 attention layers at 13.576 + 5.602 + 24.390 + 12.238 MB, over the
+# 128 launches of one token; these kernels write nothing to DRAM (their output rows stay in the L2).
+HEAD_GEMV_DRAM_BYTES_PER_LAUNCH = 327_891_968 + 4_020_096
+LAYER_GEMV_DRAM_BYTES_PER_LAUNCH = 14_518_700
 
 
 def measured_peaks() -> tuple[float, str]:
