@@ -469,7 +469,7 @@ struct Engine {
   }
 
   bool swiglu_in_gate_up(const dfb_layer_desc& L) const {
-    if (m.batch != 1 || tp() || m.math != MATH_FAST || !(L.gate_up.packed_k8 || L.gate_up.packed_mma)) return false;
+    if (m.batch != 1 || m.math != MATH_FAST || !(L.gate_up.packed_k8 || L.gate_up.packed_mma)) return false;
     GemvParams q = {};
     q.rows = 1;
     q.packed_k8 = (const uint32_t*)L.gate_up.packed_k8;
@@ -493,20 +493,21 @@ struct Engine {
     bf16* h = (bf16*)at(ws.h);
     bf16* gu = (bf16*)at(ws.gu);
     const int H = m.hidden, I = m.intermediate;
-    if (swiglu_in_gate_up(L)) {
-      // gate|up leaves bf16(silu(gate)) * up directly (a cluster holds a gate tile and the up tile of the same channels)
-      int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_SWIGLU, gu, I, nullptr, s);
-      if (rc) return rc;
-      return gemv(L.down, gu, I, PRO_NONE, nullptr, nullptr, 0, EPI_RESIDUAL, h, H, nullptr, s);
-    }
-    int rc = gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
+    // Where the kernel can, gate|up leaves bf16(silu(gate)) * up directly (a cluster holds a gate tile and the up tile of
+    // the same channels) and the down projection reads it as it is; otherwise down applies SwiGLU in its prologue.
+    const bool fused = swiglu_in_gate_up(L);
+    int rc = fused ? gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_SWIGLU, gu, I, nullptr, s)
+                   : gemv(L.gate_up, h, H, PRO_RMSNORM, L.post_norm_w, nullptr, 0, EPI_STORE, gu, 2L * I, nullptr, s);
     if (rc) return rc;
+    const long xs = fused ? I : 2L * I;
+    const int pro = fused ? PRO_NONE : PRO_SILU_MUL;
+    const bf16* up = fused ? nullptr : gu + I;
     if (peer()) {
       aim_peer(2 * i + 1);
-      return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_PARTIAL_PEER, (bf16*)at(ws.ar), H, nullptr, s);
+      return gemv(L.down, gu, xs, pro, nullptr, up, xs, EPI_PARTIAL_PEER, (bf16*)at(ws.ar), H, nullptr, s);
     }
-    if (tp()) return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
-    return gemv(L.down, gu, 2L * I, PRO_SILU_MUL, nullptr, gu + I, 2L * I, EPI_RESIDUAL, h, H, nullptr, s);
+    if (tp()) return gemv(L.down, gu, xs, pro, nullptr, up, xs, EPI_PARTIAL_F32, (bf16*)at(ws.ar), H, nullptr, s);
+    return gemv(L.down, gu, xs, pro, nullptr, up, xs, EPI_RESIDUAL, h, H, nullptr, s);
   }
 
   int head_and_pick(cudaStream_t s) {

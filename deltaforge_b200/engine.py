@@ -305,7 +305,7 @@ class DecodeEngine:
 
                 qw.k8 = ops.int4_repack_k8(qw.qweight)
             k8 = qw.k8.data_ptr() if qw.k8 is not None else None
-            wants_mma = tensor_core_gemv and layer_sized and self.batch == 1 and not persistent and tp_size == 1 and math == MATH_FAST
+            wants_mma = tensor_core_gemv and layer_sized and self.batch == 1 and not persistent and math == MATH_FAST
             if wants_mma and qw.group_size == 128 and k % 128 == 0 and (qw.mma is None or qw.mma_pair != pair):
                 from . import ops
 
