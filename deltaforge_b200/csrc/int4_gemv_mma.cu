@@ -45,6 +45,7 @@ namespace {
 constexpr int CW = 8;                // consumer warps: TN / 128 blocks of 16 columns each
 constexpr int CT = CW * 32;
 constexpr int THREADS = CT + 32;     // + the warp that issues the copies
+constexpr int QW = CW + 1;           // warps that quantise the activation: all of them
 constexpr int XB_BYTES = 16 * 8 * 2 * 4;  // activation bytes of one group: [16 word rows][8 B-columns][2 words]
 constexpr int MAX_CS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -86,6 +87,7 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory"); }
+__device__ __forceinline__ void all_sync() { asm volatile("bar.sync 3, %0;" ::"n"(THREADS) : "memory"); }
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -134,8 +136,9 @@ __device__ __forceinline__ void quantise_group(const float (&v)[4], int gl, floa
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = warp_max(amax);
-  int E = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
+  // non-negative floats order like their bit patterns: one warp-wide integer maximum instead of five shuffle steps
+  const uint32_t abits = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+  int E = abits != 0u ? (int)((abits >> 23) & 0xff) - 127 : 0;  // amax in [2^E, 2^(E+1))
   E = max(E, -100);
   const float up = __uint_as_float((uint32_t)(127 + 13 - E) << 23);  // 2^(13-E): |x| * up < 2^14
   if (lane == 0) fg[gl] = __uint_as_float((uint32_t)(127 - 13 + E - 4) << 23);  // 2^(E-13) / 16
@@ -214,14 +217,104 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
 
   bool ok = true;
   EpiPre pre = {};
+  // producer (lane 0 of the last warp): the weights never depend on earlier kernels; the ring is filled at once, later units
+  // follow, after the activation is quantised, as the consumers hand stages back
+  const uint64_t pol = make_evict_first_policy();
+  const unsigned char* src = p.packed_mma + ((size_t)tile * G + g0) * a.unit_bytes;
+  const int first_fill = min(nunits, a.stages);
   if (warp == CW) {
-    // producer: the weights never depend on earlier kernels; the ring is filled at once, later units follow as the
-    // consumers hand stages back
     if (lane == 0) {
-      const uint64_t pol = make_evict_first_policy();
-      const unsigned char* src = p.packed_mma + ((size_t)tile * G + g0) * a.unit_bytes;
-      int st = 0, round = 0;
-      for (int j = 0; j < nunits; ++j) {
+      for (int j = 0; j < first_fill; ++j) {
+        mbar_expect_tx(&full[j], (uint32_t)a.unit_bytes);
+        bulk_load(ring + (size_t)j * a.unit_bytes, src + (size_t)j * a.unit_bytes, (uint32_t)a.unit_bytes, &full[j], pol);
+      }
+      trace_mark(p.trace, cta, 7);
+    }
+    __syncwarp();
+  }
+  // Every warp, the producer's included, quantises groups of the activation (warp w: groups w, w + 9, ...).
+  // What this CTA reads that no kernel of this token writes goes in flight before the wait for the previous kernel: the
+  // norm weights of the groups it quantises, and, where the caller says the history was last written before this stream's
+  // current work began (the decode engine: one token ago), the conv taps and history its epilogue uses.
+  uint2 xraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)}, wraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+  const int my_n = t < TN ? tile_column<TN>(tile, t, p.N, 0) : -1;
+  const bool finisher = (cs == 1 || rank == 0) && !swiglu && my_n >= 0;
+  if (p.prologue == PRO_RMSNORM) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if (warp + j * QW < nunits) wraw[j] = *(const uint2*)(p.norm_w + (g0 + warp + j * QW) * 128 + lane * 4);
+  }
+  const float inv_k = __frcp_rn((float)p.K);
+  const bool conv_early = p.epilogue == EPI_CONV && p.conv_state_settled;
+  if (finisher && conv_early) pre = epilogue_preload(p, 0, my_n);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
+  if (t == 0) trace_mark(p.trace, cta, 1);
+  // Everything this CTA reads that an earlier kernel wrote goes in flight at once.
+  // (the first two groups each warp quantises: a CTA holds at most eighteen groups in practice, so this is all of them)
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+    if (warp + j * QW < nunits && p.prologue != PRO_ATTN_MERGE) {
+      const int k = (g0 + warp + j * QW) * 128 + lane * 4;
+      xraw[j] = *(const uint2*)(p.x + k);
+      if (p.prologue == PRO_SILU_MUL) wraw[j] = *(const uint2*)(p.up + k);
+    }
+  if (finisher && !conv_early) pre = epilogue_preload(p, 0, my_n);
+  float rstd = 1.f;
+  if (p.prologue == PRO_RMSNORM) {
+    float tot = 0.f;
+    if (p.ss_in && p.ss_count <= 32) {
+      // the kernel that wrote x left the sums of squares of its tiles: one load per lane and a shuffle tree (the same
+      // tree in every warp of every CTA, so all of them get the same bits), not a chain of dependent loads
+      tot = warp_sum(lane < p.ss_count ? p.ss_in[lane] : 0.f);
+    } else if (p.ss_in) {
+      for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
+    } else {
+      float ss = 0.f;
+      for (int k = t; k < p.K; k += THREADS) {
+        const float v = bf2f(p.x[k]);
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) wred[warp] = ss;
+      all_sync();
+#pragma unroll
+      for (int w = 0; w < QW; ++w) tot += wred[w];
+    }
+    // 1 / sqrt(mean + eps) by the reciprocal-square-root unit and one Newton step (within an ulp of the two correctly
+    // rounded steps the slower kernels take; the chain of dependent instructions is a third as long)
+    const float y = fmaf(tot, inv_k, p.eps);
+    const float r = rsqrtf(y);
+    rstd = r * fmaf(-0.5f * y * r, r, 1.5f);
+  }
+  // One warp per group of this CTA: shared exponent, 15-bit integers m (|m| < 2^14), cut into signed bytes in the order
+  // the mma's B fragments are read. Lane l holds rows 4l .. 4l+3 of the group = half of word row l/2.
+  for (int gl = warp; gl < nunits; gl += QW) {
+    float v[4];
+    if (p.prologue == PRO_ATTN_MERGE) {
+      attn_merge_values(p.merge, (g0 + gl) * 128 + lane * 4, v);
+    } else {
+      uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
+      if (gl >= warp + 2 * QW) {  // a third group and later: loaded here
+        const int k = (g0 + gl) * 128 + lane * 4;
+        xv = *(const uint2*)(p.x + k);
+        if (p.prologue == PRO_RMSNORM) wv = *(const uint2*)(p.norm_w + k);
+        if (p.prologue == PRO_SILU_MUL) wv = *(const uint2*)(p.up + k);
+      }
+      const float xr[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16),
+                           __uint_as_float(xv.y & 0xffff0000u)};
+      const float wr[4] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
+                           __uint_as_float(wv.y & 0xffff0000u)};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
+    }
+    quantise_group(v, gl, fg, msum, xb, lane);
+  }
+  all_sync();
+  if (t == 0) trace_mark(p.trace, cta, 2);
+  if (warp == CW) {
+    if (lane == 0) {  // the units beyond the ring's depth, each as its stage comes back
+      int st = first_fill == a.stages ? 0 : first_fill, round = first_fill == a.stages ? 1 : 0;
+      for (int j = first_fill; j < nunits; ++j) {
         if (round > 0 && !mbar_wait(&empty[st], (round - 1) & 1)) {
           atomicExch(a.status, 6);
           break;
@@ -229,90 +322,10 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
         mbar_expect_tx(&full[j], (uint32_t)a.unit_bytes);
         bulk_load(ring + (size_t)st * a.unit_bytes, src + (size_t)j * a.unit_bytes, (uint32_t)a.unit_bytes, &full[j], pol);
         if (++st == a.stages) st = 0, ++round;
-        if (j + 1 == min(nunits, a.stages)) trace_mark(p.trace, cta, 7);
       }
     }
     __syncwarp();  // the whole warp takes part in the (aligned) cluster barrier below
   } else {
-    // What this CTA reads that no kernel of this token writes goes in flight before the wait for the previous kernel: the
-    // norm weights of the groups it quantises, and, where the caller says the history was last written before this stream's
-    // current work began (the decode engine: one token ago), the conv taps and history its epilogue uses.
-    uint2 xraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)}, wraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-    const int my_n = t < TN ? tile_column<TN>(tile, t, p.N, 0) : -1;
-    const bool finisher = (cs == 1 || rank == 0) && !swiglu && my_n >= 0;
-    if (p.prologue == PRO_RMSNORM) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        if (warp + j * CW < nunits) wraw[j] = *(const uint2*)(p.norm_w + (g0 + warp + j * CW) * 128 + lane * 4);
-    }
-    const float inv_k = __frcp_rn((float)p.K);
-    const bool conv_early = p.epilogue == EPI_CONV && p.conv_state_settled;
-    if (finisher && conv_early) pre = epilogue_preload(p, 0, my_n);
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the activation comes from the previous kernel
-    if (t == 0) trace_mark(p.trace, cta, 1);
-    // Everything this CTA reads that an earlier kernel wrote goes in flight at once.
-    // (the first two groups each warp quantises: a CTA holds at most sixteen groups in practice, so this is all of them)
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-      if (warp + j * CW < nunits && p.prologue != PRO_ATTN_MERGE) {
-        const int k = (g0 + warp + j * CW) * 128 + lane * 4;
-        xraw[j] = *(const uint2*)(p.x + k);
-        if (p.prologue == PRO_SILU_MUL) wraw[j] = *(const uint2*)(p.up + k);
-      }
-    if (finisher && !conv_early) pre = epilogue_preload(p, 0, my_n);
-    float rstd = 1.f;
-    if (p.prologue == PRO_RMSNORM) {
-      float tot = 0.f;
-      if (p.ss_in && p.ss_count <= 32) {
-        // the kernel that wrote x left the sums of squares of its tiles: one load per lane and a shuffle tree (the same
-        // tree in every warp of every CTA, so all of them get the same bits), not a chain of dependent loads
-        tot = warp_sum(lane < p.ss_count ? p.ss_in[lane] : 0.f);
-      } else if (p.ss_in) {
-        for (int i = 0; i < p.ss_count; ++i) tot += p.ss_in[i];
-      } else {
-        float ss = 0.f;
-        for (int k = t; k < p.K; k += CT) {
-          const float v = bf2f(p.x[k]);
-          ss = fmaf(v, v, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) wred[warp] = ss;
-        consumer_sync();
-#pragma unroll
-        for (int w = 0; w < CW; ++w) tot += wred[w];
-      }
-      // 1 / sqrt(mean + eps) by the reciprocal-square-root unit and one Newton step (within an ulp of the two correctly
-      // rounded steps the slower kernels take; the chain of dependent instructions is a third as long)
-      const float y = fmaf(tot, inv_k, p.eps);
-      const float r = rsqrtf(y);
-      rstd = r * fmaf(-0.5f * y * r, r, 1.5f);
-    }
-    // One warp per group of this CTA: shared exponent, 15-bit integers m (|m| < 2^14), cut into signed bytes in the order
-    // the mma's B fragments are read. Lane l holds rows 4l .. 4l+3 of the group = half of word row l/2.
-    for (int gl = warp; gl < nunits; gl += CW) {
-      float v[4];
-      if (p.prologue == PRO_ATTN_MERGE) {
-        attn_merge_values(p.merge, (g0 + gl) * 128 + lane * 4, v);
-      } else {
-        uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
-        if (gl >= warp + 2 * CW) {  // a third group and later: loaded here
-          const int k = (g0 + gl) * 128 + lane * 4;
-          xv = *(const uint2*)(p.x + k);
-          if (p.prologue == PRO_RMSNORM) wv = *(const uint2*)(p.norm_w + k);
-          if (p.prologue == PRO_SILU_MUL) wv = *(const uint2*)(p.up + k);
-        }
-        const float xr[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16),
-                             __uint_as_float(xv.y & 0xffff0000u)};
-        const float wr[4] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
-                             __uint_as_float(wv.y & 0xffff0000u)};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = prologue_apply(p.prologue, xr[i], wr[i], rstd);
-      }
-      quantise_group(v, gl, fg, msum, xb, lane);
-    }
-    consumer_sync();
-    if (t == 0) trace_mark(p.trace, cta, 2);
-
     // The tile is cut into chunks of four 16-column blocks. A warp owns one chunk (warp % CH) and every (CW / CH)-th
     // unit of it, so the four blocks of a unit give it four independent chains of mma and a unit is waited for once per
     // chunk. lane = 4 * gq + tq: rows gq and gq + 8 of the mma, word row tq of every 32-row step.
