@@ -14,9 +14,12 @@
 //  * After the wait every CTA normalises and rotates the query heads of its KV head itself; the CTA
 //    whose slice holds the new position also normalises, rotates and stores the new key and value,
 //    and appends that row to its staged slice.
-//  * A warp takes every 8th staged key; a lane holds 8 of the 256 head dims. Scores, running max and
-//    sum, and the weighted values are fp32 (like the reference's own decode kernels). The loop body is
-//    one key, kept small on purpose: this kernel runs once per layer and its instructions are cold.
+//  * The slice is scanned in three passes over shared memory. Scores: a lane holds 8 of the 256 head dims and forms its
+//    part of 32 dot products (8 keys x 4 query heads); one transposing reduction of 31 shuffles finishes all 32, where
+//    a reduction per score would take 160. Softmax: one warp per query head finds the slice's maximum and sum. Values:
+//    a warp takes every 8th key, a lane 8 head dims. Everything is fp32 (like the reference's own decode kernels). The
+//    first form of this kernel reduced every score over the warp with five shuffles and kept a running maximum per
+//    warp: 10 000 cycles for 129 keys, nearly all of it shuffle latency.
 //  * Warps merge in shared memory; the CTAs of a cluster merge in the first CTA's shared memory
 //    through distributed shared memory and one cluster barrier; clusters merge through a small
 //    global buffer, finished by the last cluster to arrive.
@@ -125,16 +128,18 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   extern __shared__ __align__(128) unsigned char smraw[];
   // rows staged per slice: what the cache's capacity can ask for (at least the 32 rows' worth of bytes the warp merge reuses)
   const int cap = max((p.max_seq + (int)gridDim.x - 1) / (int)gridDim.x, AW * GROUPS * 2);
+  const int scp = (cap + 31) & ~31;               // score rows are padded to whole warps of keys
   bf16* kst = (bf16*)smraw;                       // [cap][D] staged keys
   bf16* vst = kst + cap * D;                      // [cap][D] staged values
   float* q_s = (float*)(vst + cap * D);           // [GROUPS][D] rotated queries times the softmax scale
   float* rowbuf = q_s + GROUPS * D;               // [2][D] scratch for the new key / value row
-  float* ml_s = rowbuf + 2 * D;                   // [AW][GROUPS][2]
-  float* cl_acc = ml_s + AW * GROUPS * 2;         // [MAX_CS][GROUPS][D] per-rank sums (used in rank 0)
+  float* sc = rowbuf + 2 * D;                     // [GROUPS][scp] scores of the slice
+  float* pj = sc + GROUPS * scp;                  // [scp][GROUPS] exp(score - max): what the value pass reads per key
+  float* cl_acc = pj + GROUPS * scp;              // [MAX_CS][GROUPS][D] per-rank sums (used in rank 0)
   float* cl_ml = cl_acc + MAX_CS * GROUPS * D;    // [MAX_CS][GROUPS][2]
   float* wgt = cl_ml + MAX_CS * GROUPS * 2;       // [GROUPS][16] merge weights
-  float* wgt_w = wgt + GROUPS * 16;               // [32] rescale weights of the warp merge and of the cluster merge
-  float* mlt_s = wgt_w + 32;                      // [GROUPS][2] merged (m, l)
+  float* wgt_w = wgt + GROUPS * 16;               // [32] rescale weights of the cluster merge
+  float* mlt_s = wgt_w + 32;                      // [GROUPS][2] (max, sum) of the slice, then of the cluster
   uint64_t* bar = (uint64_t*)(mlt_s + GROUPS * 2); // copy barrier
   float* acc_s = (float*)smraw;                   // [AW][GROUPS][D], reuses the staged slice after the scan
   __shared__ int s_last;
@@ -213,90 +218,100 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   __syncthreads();
   if (t == 0) trace_mark(p.trace, cta, 2);
 
-  float qr[GROUPS][8];
+  // Pass 1, scores: a lane holds 8 of the 256 head dims (rows are read as they lie, no bank conflicts) and forms its part
+  // of the dot products of a batch of keys with every query head of the group: 32 partial sums per lane. One
+  // transposing reduction (31 shuffles: at every level a lane sends the half of its values that its partner keeps)
+  // leaves lane l with the finished score number l of the batch, instead of five shuffles per score.
+  {
+    float qr[GROUPS][8];
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) qr[g][i] = q_s[g * D + lane * 8 + i];
+    constexpr int KB = 32 / GROUPS;  // keys per batch
+#pragma unroll 1
+    for (int j0 = warp * KB; j0 < n_keys; j0 += AW * KB) {
+      float v[32];
+#pragma unroll
+      for (int kk = 0; kk < KB; ++kk) {
+        float kf[8];
+        unpack8(*(const uint4*)(kst + (size_t)min(j0 + kk, n_keys - 1) * D + lane * 8), kf);
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+          float a = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a = fmaf(qr[g][i], kf[i], a);
+          v[kk * GROUPS + g] = a;
+        }
+      }
+#pragma unroll
+      for (int h = 16; h > 0; h >>= 1) {
+        const bool up = (lane & h) != 0;
+#pragma unroll
+        for (int i = 0; i < h; ++i) {
+          const float send = up ? v[i] : v[i + h], keep = up ? v[i + h] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+        }
+      }
+      const int j = j0 + lane / GROUPS;  // lane l holds value number l of the batch: key l / GROUPS, head l % GROUPS
+      if (j < n_keys) sc[(lane % GROUPS) * scp + j] = v[0];
+    }
+  }
+  __syncthreads();
+  // Pass 2, softmax of the slice: warp g takes query head g
+  if (warp < GROUPS) {
+    float mx = -INFINITY;
+    for (int i = lane; i < n_keys; i += 32) mx = fmaxf(mx, sc[warp * scp + i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < n_keys; i += 32) {
+      const float sv = sc[warp * scp + i];
+      const float pe = __expf(sv - mx);
+      pj[i * GROUPS + warp] = pe;
+      sum += pe;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      mlt_s[warp * 2] = mx;
+      mlt_s[warp * 2 + 1] = sum;
+    }
+  }
+  __syncthreads();
+  // Pass 3, values: a warp takes every 8th key, a lane 8 of the 256 head dims
+  float acc[GROUPS][8];
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qr[g][i] = q_s[g * D + lane * 8 + i];
-  float m[GROUPS], l[GROUPS], acc[GROUPS][8];
-#pragma unroll
-  for (int g = 0; g < GROUPS; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
     for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
-  }
-  // two keys per iteration: their score reductions and exponentials interleave
-#pragma unroll 1
-  for (int j = warp; j < n_keys; j += 2 * AW) {
-    const bool two = (j + AW) < n_keys;
-    const int j2 = two ? j + AW : j;
-    float kf[8], vf[8], kf2[8], vf2[8];
-    unpack8(*(const uint4*)(kst + j * D + lane * 8), kf);
-    unpack8(*(const uint4*)(vst + j * D + lane * 8), vf);
-    unpack8(*(const uint4*)(kst + j2 * D + lane * 8), kf2);
-    unpack8(*(const uint4*)(vst + j2 * D + lane * 8), vf2);
+#pragma unroll 2
+  for (int j = warp; j < n_keys; j += AW) {
+    float vf[8];
+    unpack8(*(const uint4*)(vst + (size_t)j * D + lane * 8), vf);
 #pragma unroll
     for (int g = 0; g < GROUPS; ++g) {
-      float s = 0.f, s2 = 0.f;
+      const float pe = pj[j * GROUPS + g];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        s = fmaf(qr[g][i], kf[i], s);
-        s2 = fmaf(qr[g][i], kf2[i], s2);
-      }
-      s = warp_sum(s);
-      s2 = warp_sum(s2);
-      if (!two) s2 = -INFINITY;
-      const float mn = fmaxf(m[g], fmaxf(s, s2));
-      const float corr = __expf(m[g] - mn), pe = __expf(s - mn), pe2 = __expf(s2 - mn);
-      l[g] = l[g] * corr + pe + pe2;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * corr + pe * vf[i] + pe2 * vf2[i];
-      m[g] = mn;
+      for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(pe, vf[i], acc[g][i]);
     }
   }
   __syncthreads();  // everyone is done with the staged slice; its memory becomes the warp-merge buffer
   if (t == 0) trace_mark(p.trace, cta, 3);
 
-  // merge the 8 warps: afterwards thread t owns head dim t of every query head. The AW * GROUPS rescale weights
-  // exp(m_w - max m) are computed once, by the first warp, not by every thread.
+  // add the 8 warps (one common maximum per slice: no rescaling): afterwards thread t owns head dim t of every query head
 #pragma unroll
-  for (int g = 0; g < GROUPS; ++g) {
+  for (int g = 0; g < GROUPS; ++g)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc_s[(warp * GROUPS + g) * D + lane * 8 + i] = acc[g][i];
-    if (lane == 0) {
-      ml_s[(warp * GROUPS + g) * 2] = m[g];
-      ml_s[(warp * GROUPS + g) * 2 + 1] = l[g];
-    }
-  }
-  __syncthreads();
-  if (warp == 0) {  // lane = w * GROUPS + g (AW * GROUPS <= 32)
-    const int g = lane % GROUPS, w = lane / GROUPS;
-    const bool live = lane < AW * GROUPS;
-    float mg = -INFINITY;
-#pragma unroll
-    for (int ww = 0; ww < AW; ++ww) mg = fmaxf(mg, ml_s[(ww * GROUPS + g) * 2]);
-    const float mw = live ? ml_s[(w * GROUPS + g) * 2] : -INFINITY;
-    const float e = (mw == -INFINITY) ? 0.f : __expf(mw - mg);
-    float lw = live ? ml_s[(w * GROUPS + g) * 2 + 1] * e : 0.f;
-    // sum over the warps of one group in a fixed order: lanes g, g + GROUPS, g + 2 GROUPS, ...
-#pragma unroll
-    for (int o = GROUPS; o < 32; o <<= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
-    if (live) wgt_w[lane] = e;
-    if (lane < GROUPS) {
-      mlt_s[lane * 2] = mg;
-      mlt_s[lane * 2 + 1] = lw;
-    }
-  }
   __syncthreads();
   float o[GROUPS], lt[GROUPS], mt[GROUPS];
 #pragma unroll
   for (int g = 0; g < GROUPS; ++g) {
     float og = 0.f;
 #pragma unroll
-    for (int w = 0; w < AW; ++w) og = fmaf(acc_s[(w * GROUPS + g) * D + t], wgt_w[w * GROUPS + g], og);
+    for (int w = 0; w < AW; ++w) og += acc_s[(w * GROUPS + g) * D + t];
     o[g] = og, lt[g] = mlt_s[g * 2 + 1], mt[g] = mlt_s[g * 2];
   }
+  __syncthreads();  // (mlt_s is written again by the cluster merge)
 
   // merge the CTAs of the cluster in rank 0, the same way
   if (cs > 1) {
@@ -419,10 +434,11 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
 template <int GROUPS>
 size_t step_smem(int max_seq = MAX_KEYS, int splits = 1) {
   const int cap = std::max((max_seq + splits - 1) / splits, AW * GROUPS * 2);
+  const int scp = (cap + 31) & ~31;
   const size_t stage = (size_t)2 * cap * D * 2;  // also holds the [AW][GROUPS][D] float warp-merge buffer
   const size_t merge = (size_t)AW * GROUPS * D * 4;
   return std::max(stage, merge) +
-         (size_t)(GROUPS * D + 2 * D + AW * GROUPS * 2 + MAX_CS * GROUPS * D + MAX_CS * GROUPS * 2 + GROUPS * 16 + 32 + GROUPS * 2) * 4 + 16 + 128;
+         (size_t)(GROUPS * D + 2 * D + 2 * GROUPS * scp + MAX_CS * GROUPS * D + MAX_CS * GROUPS * 2 + GROUPS * 16 + 32 + GROUPS * 2) * 4 + 16 + 128;
 }
 
 template <int GROUPS>
