@@ -62,10 +62,18 @@ __device__ __forceinline__ void attn_merge_values(const AttnMerge& a, int k, flo
   float4 pa[MAXC];
   uint2 graw = make_uint2(0u, 0u);
   if (a.gate) graw = *(const uint2*)(a.gate + (long)h * a.gateh_stride + i);
+  // volatile loads keep their order among themselves: all sixteen are issued before the first value is used. (Left to
+  // the compiler's schedule they went cluster by cluster: one trip to the L2 per cluster, 0.35 us each.)
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
-    mlv[c] = c < a.nclusters ? __ldcg(ml + c) : make_float2(-INFINITY, 0.f);
-    pa[c] = c < a.nclusters ? __ldcg((const float4*)(acc + (long)c * a.d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    mlv[c] = make_float2(-INFINITY, 0.f);
+    pa[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < a.nclusters) {
+      asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(mlv[c].x), "=f"(mlv[c].y) : "l"(ml + c));
+      asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(pa[c].x), "=f"(pa[c].y), "=f"(pa[c].z), "=f"(pa[c].w)
+                   : "l"(acc + (long)c * a.d));
+    }
   }
   float mg = -INFINITY;
 #pragma unroll

@@ -178,7 +178,9 @@ __device__ __forceinline__ void quantise_group(const float (&v)[4], int gl, floa
   }
 }
 
-template <int TN>  // TN columns per tile: 256 (two 16-column blocks per warp) or 128 (one)
+// TN columns per tile: 256 or 128. MERGE: the instance that serves the attention-merge prologue; it keeps sixteen loads in
+// flight per lane and needs more registers than the others, which stay at three CTAs per SM.
+template <int TN, bool MERGE = false>
 __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
   constexpr int CH = TN / 64;              // chunks of four 16-column blocks per tile
   constexpr int W_BYTES = TN / 16 * 1024;  // bytes of words per unit
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
   // (the first two groups each warp quantises: a CTA holds at most eighteen groups in practice, so this is all of them)
 #pragma unroll
   for (int j = 0; j < 2; ++j)
-    if (warp + j * QW < nunits && p.prologue != PRO_ATTN_MERGE) {
+    if (warp + j * QW < nunits && !MERGE) {
       const int k = (g0 + warp + j * QW) * 128 + lane * 4;
       xraw[j] = *(const uint2*)(p.x + k);
       if (p.prologue == PRO_SILU_MUL) wraw[j] = *(const uint2*)(p.up + k);
@@ -290,7 +292,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
   // the mma's B fragments are read. Lane l holds rows 4l .. 4l+3 of the group = half of word row l/2.
   for (int gl = warp; gl < nunits; gl += QW) {
     float v[4];
-    if (p.prologue == PRO_ATTN_MERGE) {
+    if (MERGE) {
       attn_merge_values(p.merge, (g0 + gl) * 128 + lane * 4, v);
     } else {
       uint2 xv = gl == warp ? xraw[0] : xraw[1], wv = gl == warp ? wraw[0] : wraw[1];
@@ -561,6 +563,8 @@ int mma_configure() {
   };
   opt_in(gemv_mma_kernel<256>);
   opt_in(gemv_mma_kernel<128>);
+  opt_in(gemv_mma_kernel<256, true>);
+  opt_in(gemv_mma_kernel<128, true>);
   if (e != cudaSuccess) return check_launch("int4 gemv (mma): shared-memory opt-in");
   return 0;
 }
@@ -591,7 +595,11 @@ int launch_gemv_mma(const GemvParams& p, int* status, cudaStream_t stream) {
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = c.tn == 256 ? cudaLaunchKernelEx(&cfg, gemv_mma_kernel<256>, a) : cudaLaunchKernelEx(&cfg, gemv_mma_kernel<128>, a);
+  cudaError_t e;
+  if (p.prologue == PRO_ATTN_MERGE)
+    e = c.tn == 256 ? cudaLaunchKernelEx(&cfg, gemv_mma_kernel<256, true>, a) : cudaLaunchKernelEx(&cfg, gemv_mma_kernel<128, true>, a);
+  else
+    e = c.tn == 256 ? cudaLaunchKernelEx(&cfg, gemv_mma_kernel<256>, a) : cudaLaunchKernelEx(&cfg, gemv_mma_kernel<128>, a);
   if (e != cudaSuccess) {
     set_error("int4 gemv (mma): launch failed: %s", cudaGetErrorString(e));
     return 1;
