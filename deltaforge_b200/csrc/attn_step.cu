@@ -103,7 +103,9 @@ __device__ __noinline__ void norm_rope_row(const bf16* src, const bf16* nw, floa
 #pragma unroll
   for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
   ss = warp_sum(ss);
-  const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(ss, (float)D), eps));
+  // 1 / sqrt(ss / 256 + eps) in two correctly rounded steps, as a CPU evaluates it: the division by 256 is exact, so one
+  // fused multiply-add rounds where the sum would, and the correctly rounded reciprocal is the correctly rounded 1 / x
+  const float rstd = __frcp_rn(__fsqrt_rn(fmaf(ss, 1.0f / (float)D, eps)));
 #pragma unroll
   for (int i = 0; i < 8; ++i) row[lane * 8 + i] = round_bf16(__fmul_rn(__fmul_rn(x[i], rstd), __fadd_rn(1.0f, w[i])));
   __syncwarp();

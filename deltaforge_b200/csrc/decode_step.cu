@@ -100,6 +100,8 @@ struct Engine {
   PStep* ps = nullptr;    // the persistent-kernel form of the step, when the model asked for it
   unsigned long long* peer_slots[TP_MAX] = {};  // tensor parallelism by peer stores: every rank's exchange buffer
   TpPeer cur_peer = {};                          // where the next EPI_PARTIAL_PEER projection writes
+  const void* next_touch[3] = {nullptr, nullptr, nullptr};  // small arrays the next projection asks the L2 for (then cleared)
+  int next_touch_bytes[3] = {0, 0, 0};
   AttnMerge cur_merge = {};                      // what the next PRO_ATTN_MERGE projection reads
   // The projections of one step in launch order, and which of them the next GEMV launch is: every kernel of
   // the batch-1 step asks the L2 for the weights of the projection `pf_dist` GEMVs ahead (0: off).
@@ -228,6 +230,10 @@ struct Engine {
     p.math = m.math;
     p.status = (int*)at(ws.status);
     if (epilogue == EPI_PARTIAL_PEER) p.peer = cur_peer;
+    for (int i = 0; i < 3; ++i) {
+      p.touch_ptr[i] = next_touch[i], p.touch_bytes[i] = next_touch_bytes[i];
+      next_touch[i] = nullptr, next_touch_bytes[i] = 0;
+    }
     if (prologue == PRO_ATTN_MERGE) p.merge = cur_merge;
     aim_prefetch(p.pf_ptr, p.pf_bytes, cursor + pf_dist);
     ++cursor;
@@ -454,6 +460,13 @@ struct Engine {
     const int H = m.hidden;
     const long pstride = L.in_proj.N;
     const bool dn = L.kind == DFB_LAYER_DELTANET;
+    if (!dn) {
+      // the attention step reads its norm weights and rotary frequencies first thing after its wait, eight times per token:
+      // they are not in the L2 by then unless somebody asks for them; the projection before it does
+      next_touch[0] = L.q_norm_w, next_touch_bytes[0] = m.head_dim * 2;
+      next_touch[1] = L.k_norm_w, next_touch_bytes[1] = m.head_dim * 2;
+      next_touch[2] = m.inv_freq, next_touch_bytes[2] = m.rotary_dim / 2 * 4;
+    }
     int rc = gemv(L.in_proj, h, H, PRO_RMSNORM, L.input_norm_w, nullptr, 0, dn ? EPI_CONV : EPI_STORE, proj, pstride, dn ? &L : nullptr, s);
     if (rc) return rc;
     rc = dn ? mixer_deltanet(L, proj, pstride, mix, s) : mixer_attention(L, proj, pstride, mix, (bf16*)at(ws.qout), s);

@@ -232,6 +232,10 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
       }
       trace_mark(p.trace, cta, 7);
     }
+    if (cta == 0 && lane >= 1 && lane <= 3 && p.touch_ptr[lane - 1] != nullptr) {
+      const char* q = (const char*)p.touch_ptr[lane - 1];
+      for (int o = 0; o < p.touch_bytes[lane - 1]; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q + o));
+    }
     __syncwarp();
   }
   // Every warp, the producer's included, quantises groups of the activation (warp w: groups w, w + 9, ...).

@@ -101,7 +101,11 @@ struct GemvParams {
   TpPeer peer;  // EPI_PARTIAL_PEER only
   // Optional: up to two byte ranges (the words and the scales of the GEMV that follows in the step) that the
   // CTAs of this launch ask the L2 to fetch, a slice each, once their own loads are issued.
-  const void* pf_ptr[2];
+// up to three small arrays a LATER kernel of the stream reads first thing after its dependency wait (norm weights, rotary
+  // frequencies): one CTA of this launch asks the L2 for them, so that the later kernel finds them there
+  const void* touch_ptr[3];
+  int touch_bytes[3];
+    const void* pf_ptr[2];
   size_t pf_bytes[2];
   Trace trace;
   AttnMerge merge;  // PRO_ATTN_MERGE only
