@@ -105,7 +105,7 @@ def test_32_layer_step_with_a_4096_token_cache_against_the_oracle(full_model):
     caches = {m: E.DecodeCache(cfg, 1, max_seq, device=DEV) for m in ("fast", "exact")}
     synth.fill_cache(caches["fast"], context, seed=99)
     caches["exact"].load_from(caches["fast"])
-    oracle = oracle_from_weights(weights)
+    oracle = oracle_from_weights(weights, memo=True)  # 32 positions: the dequantised weights are kept between them
     ocache = oracle_cache_like(oracle, caches["fast"])
     engines = {
         "fast": E.DecodeEngine(weights, caches["fast"], math=E.MATH_FAST),
