@@ -315,6 +315,17 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
   }
   __syncthreads();  // (mlt_s is written again by the cluster merge)
 
+  // With the last merge left to the output projection, one cluster per KV head also leaves the output gate, already
+  // activated: bf16(sigmoid(fp32(gate))) (src/deltaforge/reference.py:558-568). It depends on nothing computed here, so
+  // it is evaluated now, while the other CTAs of the cluster arrive at the barrier, and not after it on the way out.
+  const bool early_gate = p.defer_merge && S / cs > 1 && split / cs == 0 && rank == 0 && p.attn_output_gate;
+  if (early_gate) {
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      const float gv = gate_v[g];
+      p.out[(long)b * p.out_stride + (long)(hk * GROUPS + g) * D + t] = f2bf(p.gate_swish ? silu_f(gv) : sigmoid_f(gv));
+    }
+  }
   // merge the CTAs of the cluster in rank 0, the same way
   if (cs > 1) {
 #pragma unroll
@@ -368,15 +379,7 @@ __global__ void __launch_bounds__(AW * 32) attn_step_kernel(const AttnStepParams
       }
     }
     if (p.defer_merge) {  // the output projection merges the clusters' partial results while it builds its activation
-      if (cidx == 0 && p.attn_output_gate) {
-        // ... and multiplies by the output gate, which one cluster per KV head leaves in `out` already activated:
-        // bf16(sigmoid(fp32(gate))) (src/deltaforge/reference.py:558-568)
-#pragma unroll
-        for (int g = 0; g < GROUPS; ++g) {
-          const float gv = gate_v[g];
-          p.out[(long)b * p.out_stride + (long)(hq0 + g) * D + t] = f2bf(p.gate_swish ? silu_f(gv) : sigmoid_f(gv));
-        }
-      }
+      // (... and multiplies by the output gate, which one cluster per KV head has left in `out`, see above)
       if (t == 0) trace_mark(p.trace, cta, 6);
       return;
     }

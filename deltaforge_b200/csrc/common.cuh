@@ -23,7 +23,7 @@ __device__ __forceinline__ float round_bf16(float v) { return bf2f(f2bf(v)); }
 __device__ __forceinline__ float silu_f(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float sigmoid_f(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 // 1 / sqrt(x) as two correctly rounded steps, which is how a CPU evaluates rsqrt.
-__device__ __forceinline__ float rsqrt_2step(float x) { return __frcp_rn(__fsqrt_rn(x)); }  // rcp.rn(s) is the correctly rounded 1 / s
+__device__ __forceinline__ float rsqrt_2step(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
 // log(1 + exp(x)) with torch's threshold of 20 above which softplus is the identity.
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 

@@ -110,8 +110,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
 
   // constants of the layer (never written by a kernel): in flight before the wait
   const float nw = col_ok ? p.norm_w[col] : 0.f;
-  const float neg_exp_a = -expf(p.a_log[hv]), dt_bias = p.dt_bias[hv];
-  const float inv_dv = (dv & (dv - 1)) == 0 ? 1.0f / (float)dv : 0.f;  // a power of two: dividing by it is an exact multiply
+  const float a_log = p.a_log[hv], dt_bias = p.dt_bias[hv];
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (t == 0) trace_mark(p.trace, cta, 1);
@@ -129,9 +128,12 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   {
     const float ss = warp_sum(x * x);
     if (lane == 0) wred[warp] = ss;
-    // the gates, by two threads of the last warp while the sums of squares are gathered
-    if (t == DN_WARPS * 32 - 1) gates[0] = round_bf16(sigmoid_f(b_logit));
-    if (t == DN_WARPS * 32 - 2) gates[1] = expf(__fmul_rn(neg_exp_a, softplus_f(__fadd_rn(a_logit, dt_bias))));
+    if (t == DN_WARPS * 32 - 1) {  // the gates, by a thread of the last warp while the sums of squares are gathered
+      const float beta = round_bf16(sigmoid_f(b_logit));
+      const float g = __fmul_rn(-expf(a_log), softplus_f(__fadd_rn(a_logit, dt_bias)));
+      gates[0] = beta;
+      gates[1] = expf(g);
+    }
     __syncthreads();
     float tot = 0.f;
     const int w0 = is_k ? DN_WARPS / 2 : 0;
@@ -169,8 +171,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) deltanet_fused_kernel(const Del
   float tot = 0.f;
   for (int rk = 0; rk < nvb; ++rk) tot += cluster_ss[rk];
   if (warp == 0 && col_ok) {
-    const float mean = inv_dv != 0.f ? __fmul_rn(tot, inv_dv) : __fdiv_rn(tot, (float)dv);
-    const float rstd = rsqrt_2step(__fadd_rn(mean, p.eps));
+    const float rstd = rsqrt_2step(__fadd_rn(__fdiv_rn(tot, (float)dv), p.eps));
     const float nrm = round_bf16(__fmul_rn(ob, rstd));
     float y = __fmul_rn(nw, nrm);
     if (p.norm_w_bf16) y = round_bf16(y);

@@ -142,31 +142,24 @@ __device__ __forceinline__ void quantise_group(const float (&v)[4], int gl, floa
   E = max(E, -100);
   const float up = __uint_as_float((uint32_t)(127 + 13 - E) << 23);  // 2^(13-E): |x| * up < 2^14
   if (lane == 0) fg[gl] = __uint_as_float((uint32_t)(127 - 13 + E - 4) << 23);  // 2^(E-13) / 16
-  int ms = 0;
-  uint32_t e0 = 0, e1 = 0, e2 = 0, o0 = 0, o1 = 0;  // this lane's halves (16 bits: two rows each) of the five B words
+  // Signed byte-pieces without a carry chain: q = p0 + 256 p1 + 65536 p2 with every p in [-128, 127] is the same as
+  // q + 0x808080 in plain unsigned bytes with 128 taken off each, i.e. with each byte's top bit flipped.
+  int m[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = __float2int_rn(v[i] * up);
-    ms += m;
-    const int sh = (i >> 1) * 8;  // rows 4l+0, 4l+1 -> byte 0 of the half; rows 4l+2, 4l+3 -> byte 1
-    if ((i & 1) == 0) {  // even row: the three signed byte-pieces of 16 m
-      const int q = m * 16;
-      const int p0 = (int)(signed char)(q & 0xff);
-      const int r1 = (q - p0) >> 8;
-      const int p1 = (int)(signed char)(r1 & 0xff);
-      const int p2 = (r1 - p1) >> 8;
-      e0 |= (uint32_t)(p0 & 0xff) << sh, e1 |= (uint32_t)(p1 & 0xff) << sh, e2 |= (uint32_t)(p2 & 0xff) << sh;
-    } else {  // odd row: the two signed byte-pieces of m
-      const int l0 = (int)(signed char)(m & 0xff);
-      const int h0 = (m - l0) >> 8;
-      o0 |= (uint32_t)(l0 & 0xff) << sh, o1 |= (uint32_t)(h0 & 0xff) << sh;
-    }
-  }
+  for (int i = 0; i < 4; ++i) m[i] = __float2int_rn(v[i] * up);
+  int ms = (m[0] + m[1]) + (m[2] + m[3]);
+  // rows 4l+0, 4l+2 (even: the three pieces of 16 m) and 4l+1, 4l+3 (odd: the two pieces of m); byte 3 of each is zero
+  const uint32_t t0 = ((uint32_t)(m[0] * 16 + 0x808080) ^ 0x808080u) & 0xffffffu, t2 = ((uint32_t)(m[2] * 16 + 0x808080) ^ 0x808080u) & 0xffffffu;
+  const uint32_t u1 = ((uint32_t)(m[1] + 0x8080) ^ 0x8080u) & 0xffffu, u3 = ((uint32_t)(m[3] + 0x8080) ^ 0x8080u) & 0xffffu;
+  // this lane's halves (16 bits: two rows each) of the five B words: rows 4l+0, 4l+1 -> byte 0 of the half, rows 4l+2,
+  // 4l+3 -> byte 1; even lanes own the low half of the word (rows 0..3 of word row l / 2), odd lanes the high half
+  const bool hi = (lane & 1) != 0;
+  uint32_t e0 = __byte_perm(t0, t2, hi ? 0x4033 : 0x3340), e1 = __byte_perm(t0, t2, hi ? 0x5133 : 0x3351);
+  uint32_t e2 = __byte_perm(t0, t2, hi ? 0x6233 : 0x3362);
+  uint32_t o0 = __byte_perm(u1, u3, hi ? 0x4033 : 0x3340), o1 = __byte_perm(u1, u3, hi ? 0x5133 : 0x3351);
   ms = (int)__reduce_add_sync(0xffffffffu, ms);
   if (lane == 0) msum[gl] = ms;
-  // lanes 2r (rows 0..3 of word row r: bytes 0, 1) and 2r+1 (rows 4..7: bytes 2, 3) complete each other's words
-  const int hs = (lane & 1) * 16;
-  e0 <<= hs, e1 <<= hs, e2 <<= hs, o0 <<= hs, o1 <<= hs;
+  // lanes 2r and 2r+1 complete each other's words
   e0 |= __shfl_xor_sync(0xffffffffu, e0, 1), e1 |= __shfl_xor_sync(0xffffffffu, e1, 1), e2 |= __shfl_xor_sync(0xffffffffu, e2, 1);
   o0 |= __shfl_xor_sync(0xffffffffu, o0, 1), o1 |= __shfl_xor_sync(0xffffffffu, o1, 1);
   // B column c of word row kb: (b0, b1) at xb[group][kb][c]; columns 3..7 are zero
