@@ -131,7 +131,13 @@ struct Engine {
     if (pf_dist <= 0 || m.batch != 1 || m.tp_size > 1 || idx < 0 || idx >= (int)order.size()) return;
     const dfb_linear& l = *order[idx];
     const size_t wbytes = (size_t)l.K * l.N / 2;
-    if (!l.packed_k8 || wbytes > ((size_t)48 << 20)) return;
+    if (wbytes > ((size_t)48 << 20)) return;
+    if (l.packed_mma) {  // the copy the tensor-core GEMV reads: words and scales in one buffer
+      ptr[0] = l.packed_mma;
+      bytes[0] = mma_repack_bytes(l.K, l.N, l.mma_pair, l.scale_is_bf16);
+      return;
+    }
+    if (!l.packed_k8) return;
     ptr[0] = l.packed_k8;
     bytes[0] = wbytes;
     ptr[1] = l.scale;

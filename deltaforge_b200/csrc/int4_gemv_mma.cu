@@ -225,6 +225,8 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MmaArgs a) {
       }
       trace_mark(p.trace, cta, 7);
     }
+    if (lane >= 4 && lane <= 5 && p.pf_ptr[lane - 4] != nullptr)  // a slice of a later projection's weights, into the L2
+      l2_prefetch_range(p.pf_ptr[lane - 4], p.pf_bytes[lane - 4] * (size_t)cta / gridDim.x, p.pf_bytes[lane - 4] * (size_t)(cta + 1) / gridDim.x);
     if (cta == 0 && lane >= 1 && lane <= 3 && p.touch_ptr[lane - 1] != nullptr) {
       const char* q = (const char*)p.touch_ptr[lane - 1];
       for (int o = 0; o < p.touch_bytes[lane - 1]; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q + o));
