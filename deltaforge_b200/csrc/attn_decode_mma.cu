@@ -99,6 +99,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const _
   uint64_t* empty = full + MSTAGES;                              // [MSTAGES]
   volatile int* failed = (volatile int*)(empty + MSTAGES);
   int* s_last = (int*)(empty + MSTAGES) + 1;
+  // tiles the producer has issued so far. A compute warp takes every 8th tile of a 12-stage ring, so it meets a stage only
+  // every other round, and a parity wait cannot tell "this round has landed" from "the round before the last has": it waits
+  // for the tile to be issued first, after which the stage's barrier is in exactly this round's phase.
+  volatile int* issued = (volatile int*)(empty + MSTAGES) + 2;
 
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
@@ -108,6 +112,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const _
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty[s])));
     }
     *failed = 0;
+    *issued = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -141,6 +146,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const _
           tma_box(st + bx * BOXB, &kmap, bx * 64, key0, hk, b, &full[s]);
           tma_box(st + (4 + bx) * BOXB, &vmap, bx * 64, key0, hk, b, &full[s]);
         }
+        *issued = tl + 1;
       }
     }
   } else {
@@ -161,6 +167,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const _
     float z[2] = {0.f, 0.f};  // rows 8..15 of every accumulator tile: always zero, shared by all MMAs
     for (int tl = warp; tl < ntiles; tl += MW) {
       const int s = tl % MSTAGES;
+      if (*issued <= tl) {  // (the usual case is that the producer is far ahead)
+        const long long t0 = clock64();
+        while (*issued <= tl && !*failed)
+          if (clock64() - t0 > MMA_WAIT_CYCLES) *failed = 1;
+        if (*failed) break;
+      }
       if (!mma_wait(&full[s], (tl / MSTAGES) & 1, failed)) break;
       unsigned char* st = ring + (size_t)s * TILEB;
       const int key0 = k_begin + tl * TK, n = min(TK, k_end - key0);
@@ -314,7 +326,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) attn_decode_mma_kernel(const _
 
 template <int GROUPS>
 size_t mma_smem() {
-  return (size_t)MSTAGES * TILEB + (size_t)(MW * GROUPS * 2 + GROUPS * MMA_MAX_SPLITS) * 4 + 2 * MSTAGES * 8 + 16 + 1024;
+  return (size_t)MSTAGES * TILEB + (size_t)(MW * GROUPS * 2 + GROUPS * MMA_MAX_SPLITS) * 4 + 2 * MSTAGES * 8 + 32 + 1024;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -190,6 +190,33 @@ def test_batch_of_eight_runs_the_tensor_core_projections_and_matches_oracle():
     assert eng.launches_per_step == 1 + 3 * 9 + 9 + 4
 
 
+def test_long_slices_of_many_sequences_decode_position_after_position_with_a_clear_status():
+    """32 sequences with 32K tokens each: the tensor-core attention kernel streams 4096-key slices through a 12-stage ring
+    of which a warp meets every stage only every other round. A warp that got two rounds ahead of a stage once took a
+    stale tile for its own (the parity of the round it waited for matched the last but one), the ring lost step, and
+    a wait ran into its limit (137 ms, status 41) at about one position in eight. 48 consecutive positions, two
+    attention layers: no status, and no step anywhere near the limit."""
+    import time
+
+    cfg = qwen_width_config(layers=8, vocab=2048)
+    weights = synth.random_model_weights(cfg, seed=21, device=DEV, scale_dtype=torch.bfloat16)
+    cache = E.DecodeCache(cfg, 32, 32768 + 64, device=DEV)
+    synth.fill_cache(cache, 32768, seed=22)
+    eng = E.DecodeEngine(weights, cache)
+    tok = torch.full((32,), 5, dtype=torch.int64, device=DEV)
+    eng.decode(tok, 2)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for _ in range(48):
+        t0 = time.perf_counter()
+        eng.decode(tok, 1)
+        torch.cuda.synchronize()
+        worst = max(worst, time.perf_counter() - t0)
+    eng.check_status()
+    assert bool(torch.isfinite(eng.logits.float()).all())
+    assert worst < 0.06, f"a step took {worst * 1e3:.1f} ms"
+
+
 def test_graph_replay_equals_plain_launches_and_is_repeatable():
     cfg = qwen_width_config(layers=4, vocab=2048)
     w = synth.random_model_weights(cfg, seed=3, device=DEV, scale_dtype=torch.float32)
