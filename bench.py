@@ -339,6 +339,7 @@ def run_ours(args) -> dict | None:
             eng.decode(tok, min(steps, 256))
             torch.cuda.synchronize()
     barrier()
+    eng.check_status()  # a kernel whose bounded wait gave up makes the number meaningless: raise, do not print it
     finite = bool(torch.isfinite(eng.logits.float()).all())
 
     # end to end through the C ABI with host buffers
@@ -353,6 +354,7 @@ def run_ours(args) -> dict | None:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
+    eng.check_status()
     same = bool(torch.equal(out_host.t().to(dev), generated))
 
     times = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
