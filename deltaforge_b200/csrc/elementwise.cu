@@ -12,6 +12,8 @@ namespace {
 __global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* x, const bf16* res, const bf16* w, float eps, int n,
                                                        bf16* resid_out, bf16* out) {
   __shared__ float wred[8];
+  pdl_launch_dependents();
+  pdl_wait();  // launched with programmatic dependent launch: everything it reads comes from the kernel before it
   const long row = blockIdx.x;
   const bf16* xr = x + row * n;
   float ss = 0.f;
@@ -87,6 +89,8 @@ __global__ void causal_conv_step_kernel(const bf16* x, bf16* cache, const bf16* 
 // Row-strided forms for the batched decode step: gate | up live side by side in one projection row, and
 // the conv runs in place on the leading channels of the input-projection row.
 __global__ void silu_mul_rows_kernel(const bf16* gate, const bf16* up, long in_stride, int n, long total, bf16* out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long r = i / n, c = i % n;
@@ -95,6 +99,8 @@ __global__ void silu_mul_rows_kernel(const bf16* gate, const bf16* up, long in_s
 }
 
 __global__ void causal_conv_rows_kernel(bf16* x, long x_stride, bf16* cache, const bf16* w, int channels, long total) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long r = i / channels;
@@ -305,14 +311,16 @@ __global__ void advance_kernel(int* pos, int by) {
 
 int launch_rms_norm(const bf16* x, const bf16* w, float eps, int rows, int n, bf16* out, cudaStream_t s) {
   if (rows <= 0) return 0;
-  rms_norm_kernel<<<rows, 256, 0, s>>>(x, nullptr, w, eps, n, nullptr, out);
+  if (launch_pdl(rms_norm_kernel, dim3(rows), dim3(256), 0, s, x, (const bf16*)nullptr, w, eps, n, (bf16*)nullptr, out) != cudaSuccess)
+    return check_launch("rms_norm");
   return check_launch("rms_norm");
 }
 
 int launch_add_rms_norm(const bf16* x, const bf16* res, const bf16* w, float eps, int rows, int n, bf16* resid_out,
                         bf16* out, cudaStream_t s) {
   if (rows <= 0) return 0;
-  rms_norm_kernel<<<rows, 256, 0, s>>>(x, res, w, eps, n, resid_out, out);
+  if (launch_pdl(rms_norm_kernel, dim3(rows), dim3(256), 0, s, x, res, w, eps, n, resid_out, out) != cudaSuccess)
+    return check_launch("add_rms_norm");
   return check_launch("add_rms_norm");
 }
 
@@ -341,14 +349,16 @@ int launch_causal_conv_step(const bf16* x, bf16* cache, const bf16* w, int batch
 int launch_silu_mul_rows(const bf16* gate, const bf16* up, long in_stride, int rows, int n, bf16* out, cudaStream_t s) {
   const long total = (long)rows * n;
   if (total <= 0) return 0;
-  silu_mul_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(gate, up, in_stride, n, total, out);
+  if (launch_pdl(silu_mul_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, gate, up, in_stride, n, total, out) != cudaSuccess)
+    return check_launch("silu_mul (rows)");
   return check_launch("silu_mul (rows)");
 }
 
 int launch_causal_conv_rows(bf16* x, long x_stride, bf16* cache, const bf16* w, int rows, int channels, cudaStream_t s) {
   const long total = (long)rows * channels;
   if (total <= 0) return 0;
-  causal_conv_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(x, x_stride, cache, w, channels, total);
+  if (launch_pdl(causal_conv_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, x, x_stride, cache, w, channels, total) != cudaSuccess)
+    return check_launch("causal conv (rows)");
   return check_launch("causal_conv_step (rows)");
 }
 

@@ -165,13 +165,24 @@ __global__ void __launch_bounds__(TC_THREADS, 2) int4_gemm_tc_kernel(const __gri
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();  // the next kernel may set itself up; it waits for this grid before it touches its inputs
 
   if (warp == DQ_WARPS) {
     // ---------------- producer: packed words of the slab and the activation tile of every k block ----------------
     if (lane == 0) {
-      for (int i = 0; i < nblocks; ++i) {
+      // The weights never depend on earlier kernels: the first ring of packed words goes in flight before the wait for the
+      // kernel that writes the activation (this kernel is launched with programmatic dependent launch).
+      const int pre = min(nblocks, a.stages);
+      for (int i = 0; i < pre; ++i) {
+        unsigned char* st = sm + (size_t)i * stage_bytes;
+        mbar_expect_tx(&full[i], PK_BYTES + b_bytes);
+        tma_load_2d(st + A_BYTES + b_bytes, &wmap, n0, (kb0 + i) * (BK / 8), &full[i]);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) tma_load_2d(sm + (size_t)i * stage_bytes + A_BYTES, &xmap, (kb0 + i) * BK, 0, &full[i]);
+      for (int i = pre; i < nblocks; ++i) {
         const int s = i % a.stages;
-        if (i >= a.stages && !tc_wait(&freed[s], ((i / a.stages) - 1) & 1, failed, a.status, 31)) break;
+        if (!tc_wait(&freed[s], ((i / a.stages) - 1) & 1, failed, a.status, 31)) break;
         unsigned char* st = sm + (size_t)s * stage_bytes;
         mbar_expect_tx(&full[s], PK_BYTES + b_bytes);
         tma_load_2d(st + A_BYTES + b_bytes, &wmap, n0, (kb0 + i) * (BK / 8), &full[s]);
@@ -419,7 +430,8 @@ int launch_gemm_tc(const GemvParams& p, int* status, cudaStream_t stream) {
   }
   const size_t smem = (size_t)a.stages * stage_bytes + (3 * a.stages + 1) * 8 + 64 + 1024;
   dim3 grid((p.N + TM - 1) / TM, a.splits, 1);
-  int4_gemm_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(wmap, xmap, a);
+  if (launch_pdl(int4_gemm_tc_kernel, grid, dim3(TC_THREADS), smem, stream, wmap, xmap, a) != cudaSuccess)
+    return check_launch("int4 gemm (tensor core)");
   return check_launch("int4 gemm (tensor core)");
 }
 
