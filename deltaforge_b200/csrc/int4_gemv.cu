@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(NWARP * 32) gemv_g128_kernel(const GemvParams 
   float* wsum = (float*)(xs_h + ROWS * 2 * 128);      // [ROWS][NWARP] per-warp activation sums
   float* wscr = wsum + ROWS * NWARP;                  // [NWARP] scratch for the row statistic
   __shared__ int s_last;
+  __shared__ float wmaxs[ROWS * NWARP];  // per-warp largest |activation|
+  __shared__ float upf[ROWS * 2];        // power of two each half-group's fp16 activations were scaled down by
 
   const int tile = blockIdx.x, g = blockIdx.y, zb = blockIdx.z;
   const int G = p.K / 256, half = p.K / 2;
@@ -102,12 +104,38 @@ __global__ void __launch_bounds__(NWARP * 32) gemv_g128_kernel(const GemvParams 
       v = prologue_value(p, row, kind * half + g * GROUP_ROWS + j, rstd);
     }
     xs_f[r * 256 + t] = v;
-    __half hv = __float2half_rn(v);
-    xs_h[r * 256 + t] = hv;
-    float s = warp_sum(MATH == MATH_EXACT ? v : __half2float(hv));
-    if (lane == 0) wsum[r * NWARP + warp] = s;
+    if (MATH == MATH_EXACT) {
+      const float s = warp_sum(v);
+      if (lane == 0) wsum[r * NWARP + warp] = s;
+    } else {
+      const float am = warp_max(fabsf(v));
+      if (lane == 0) wmaxs[r * NWARP + warp] = am;
+    }
   }
   __syncthreads();
+  if (MATH != MATH_EXACT) {
+    // The fp16 forms keep the activation as fp16. A half-group (128 values) whose largest magnitude reaches 2^14 (2^10
+    // in the packed-fp16 form) is scaled down by a power of two first, so that nothing overflows (65504) where the reference's bf16 stays finite;
+    // the factor goes back on after the group's sum. Below that nothing is scaled and the bits are what they were.
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int kind = t >> 7;
+      float gm = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < 4; ++wq) gm = fmaxf(gm, wmaxs[r * NWARP + kind * 4 + wq]);
+      const int ex = (int)((__float_as_uint(gm) >> 23) & 0xff) - 127;  // gm in [2^ex, 2^(ex+1))
+      // (the packed-fp16 form also adds four products of up to 8 |x| in fp16: it needs |x| < 2^10)
+      const int top = MATH == MATH_FAST_HALF2 ? 10 : 14;
+      const int e = (ex >= top && ex < 128) ? ex - (top - 1) : 0;
+      const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+      if ((t & 127) == 0) upf[r * 2 + kind] = __uint_as_float((uint32_t)(127 + e) << 23);
+      const __half hv = __float2half_rn(xs_f[r * 256 + t] * down);
+      xs_h[r * 256 + t] = hv;
+      const float s = warp_sum(__half2float(hv));
+      if (lane == 0) wsum[r * NWARP + warp] = s;
+    }
+    __syncthreads();
+  }
 
   // 3. Multiply-accumulate this warp's 16 rows.
   float accL[ROWS][8], accH[ROWS][8];
@@ -264,7 +292,7 @@ __global__ void __launch_bounds__(NWARP * 32) gemv_g128_kernel(const GemvParams 
         vL = fmaf(-1032.f, sxL, vL);
         vH = fmaf(-72.f, sxH, vH * 0.0625f);
       }
-      val[r] = (MATH == MATH_EXACT) ? (vL + vH) : fmaf(sl, vL, sh * vH);
+      val[r] = (MATH == MATH_EXACT) ? (vL + vH) : fmaf(sl * upf[r * 2], vL, sh * upf[r * 2 + 1] * vH);
     }
   }
 

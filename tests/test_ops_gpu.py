@@ -123,6 +123,29 @@ GEMV_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("rows", [1, 4])
+@pytest.mark.parametrize("math", [ops.MATH_FAST, ops.MATH_FAST_HALF2])
+def test_gemv_with_activations_beyond_the_fp16_range(rows, math):
+    """Activations of a few 1e5 (the SwiGLU output of a real checkpoint has such channels): the kernels that hold the
+    activation as fp16 scale a group down by a power of two first, so the result stays finite and as close to the
+    exact product as with ordinary activations; a group of ordinary size next to it is untouched."""
+    k, n = 2560, 1024
+    packed, scale, group = random_int4(k, n, 4242)
+    x = torch.randn((rows, 1, k), generator=gen(5))
+    x[..., 256:384] *= 2.0e5  # one scale group far beyond 65504
+    x[..., 1300] = -9.0e4     # and a single channel in another
+    x = x.to(BF16)
+    truth = R.dequant_gemv_int4_fp32(x, packed, scale, group).reshape(rows, 1, n)
+    got = ops.int4_gemv_fused(x.to(DEV), packed.to(DEV), scale.to(DEV), group, math=math)
+    assert bool(torch.isfinite(got.float()).all())
+    err = (got.double().cpu() - truth).abs()
+    rms = truth.pow(2).mean().sqrt()
+    # (one group dominates every output, so outputs of four or five times the rms occur: the bf16 rounding of the result
+    # alone is half a step of 2^-8 of those)
+    assert (err.max() / rms).item() < 4e-2
+    assert (err.pow(2).mean().sqrt() / rms).item() < 4e-3
+
+
 @pytest.mark.parametrize("rows,k,n", GEMV_SHAPES)
 @pytest.mark.parametrize("math", [ops.MATH_FAST, ops.MATH_EXACT, ops.MATH_FAST_HALF2])
 def test_gemv_against_oracle(rows, k, n, math):
