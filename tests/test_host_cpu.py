@@ -37,6 +37,37 @@ def test_library_exports_every_declared_symbol():
     assert lib.dfb_last_error() is not None
 
 
+def test_header_is_plain_c_and_a_c_program_can_bind_the_library(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 and as C++11 on its own, and a C program that includes it
+    must link against the library and call an entry point that needs no device."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler here")
+    header = ROOT / "include" / "dfb200.h"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c", str(header)], check=True)
+    gxx = shutil.which("g++")
+    if gxx is not None:
+        subprocess.run([gxx, "-std=c++11", "-fsyntax-only", "-x", "c++", str(header)], check=True)
+    lib = _lib.library_path()
+    _lib.load()  # builds it if it is missing
+    src = tmp_path / "bind.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "dfb200.h"\n'
+        "int main(void) {\n"
+        "  if (dfb_abi_version() != 1) return 1;\n"
+        "  if (dfb_int4_gemv(0, 0) != 2) return 2; /* null descriptor: a bad-argument code, no device touched */\n"
+        '  printf("%zu\\n", dfb_int4_gemv_scratch_bytes(4, 2560, 2560, 128));\n'
+        "  return 0;\n}\n"
+    )
+    exe = tmp_path / "bind"
+    subprocess.run([gcc, "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe), str(lib), f"-Wl,-rpath,{lib.parent}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    assert int(out.strip()) > 4 * 10 * 2560 * 4
+
+
 def test_scratch_size_queries_need_no_device():
     lib = _lib.load()
     assert lib.dfb_int4_gemv_scratch_bytes(1, 64, 40, 32) == 0  # generic path: no scratch
