@@ -313,7 +313,7 @@ def run_ours(args) -> dict | None:
     cache = E.DecodeCache(cfg, BATCH, CONTEXT + steps + warmup + 8, device=dev)
     synth.fill_cache(cache, CONTEXT, seed=77 + rank)
     snap = cache.snapshot()
-    eng = E.DecodeEngine(weights, cache, persistent=args.engine == "persistent", prefetch_distance=args.prefetch_distance,
+    eng = E.DecodeEngine(weights, cache, prefetch_distance=args.prefetch_distance,
                          tensor_core_gemv=not args.no_tensor_core_gemv)
     tok = torch.full((BATCH,), 1000 + rank, dtype=torch.int64, device=dev)
     eng.capture()
@@ -365,7 +365,7 @@ def run_ours(args) -> dict | None:
     head_ms, head_bytes = time_head_gemv(weights) if rank == 0 else (0.0, 0)
     launches_per_step, attn_splits = eng.launches_per_step, eng.attn_splits
     proj_stats = None
-    if rank == 0 and args.engine == "graph":
+    if rank == 0:
         # After every timed region: re-capture the step with the kernels' per-CTA timestamp marks on, run a few tokens, and
         # read the last one launch by launch. A launch's time is its share of the step's critical path: from the last
         # exit of the launch before it to its own last exit.
@@ -424,7 +424,7 @@ def run_ours(args) -> dict | None:
             "sequences": world * BATCH,
             "parallelism": f"independent sequences x{world}, no collectives",
             "l2": "each step streams 2.4 GB of weights, KV and state, 19x the 126 MB L2; no flush needed",
-            "engine": args.engine,
+            "engine": "graph",
             "attn_splits": attn_splits,
             "scale_dtype": "bf16",
         },
@@ -641,8 +641,6 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU port leg of the default run")
-    ap.add_argument("--engine", choices=("graph", "persistent"), default="graph",
-                    help="graph: one CUDA graph of kernels per token; persistent: one persistent kernel per token")
     ap.add_argument(
         "--layers",
         type=int,

@@ -94,7 +94,7 @@ class ModelDesc(C.Structure):
         ("layers_host", C.POINTER(LayerDesc)),
         ("tokens", c_vp), ("history", c_vp), ("pos", c_vp), ("logits", c_vp),
         ("workspace", c_vp), ("workspace_bytes", c_sz), ("attn_splits", c_i32), ("math", c_i32),
-        ("persistent", c_i32), ("weight_stream", c_vp), ("weight_stream_bytes", c_sz), ("tp_size", c_i32), ("tp_rank", c_i32), ("tp_peer_slots", C.POINTER(c_vp)),
+        ("tp_size", c_i32), ("tp_rank", c_i32), ("tp_peer_slots", C.POINTER(c_vp)),
     ]  # fmt: skip
 
 
@@ -125,13 +125,10 @@ SIGNATURES = {
     "dfb_attn_prep": (C.c_int, [C.POINTER(AttnPrepDesc), c_vp]),
     "dfb_attn_step": (C.c_int, [C.POINTER(AttnStepDesc), c_vp]),
     "dfb_engine_workspace_bytes": (c_sz, [C.POINTER(ModelDesc)]),
-    "dfb_engine_weight_stream_bytes": (c_sz, [C.POINTER(ModelDesc)]),
     "dfb_engine_num_segments": (C.c_int, [c_vp]),
     "dfb_engine_step_segment": (C.c_int, [c_vp, C.c_int, c_vp]),
     "dfb_engine_partial_buffer": (c_vp, [c_vp]),
     "dfb_engine_tp_exchange_bytes": (c_sz, [C.c_int, C.c_int, C.c_int]),
-    "dfb_engine_trace_layer": (C.c_int, [c_vp, C.c_int]),
-    "dfb_engine_read_trace": (C.c_int, [c_vp, c_vp, C.c_int, c_vp]),
     "dfb_engine_create": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(c_vp)]),
     "dfb_engine_destroy": (C.c_int, [c_vp]),
     "dfb_engine_step": (C.c_int, [c_vp, c_vp]),

@@ -37,7 +37,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, ar, epoch, pstep, total;
+  size_t h, proj, mix, qout, gu, partials, counters, attn, am_val, am_idx, am_ctr, status, h_ss, xn, ar, epoch, total;
 };
 
 size_t linear_partials(const dfb_linear& l, int rows) { return gemv_partials_bytes(rows, l.K, l.N, l.group); }
@@ -84,7 +84,6 @@ Workspace plan(const dfb_model_desc& m) {
   w.xn = take(m.batch >= 8 ? B * std::max(std::max((size_t)m.hidden, (size_t)m.intermediate), mixw) * 2 : 0);
   w.ar = take(m.tp_size > 1 ? B * m.hidden * 4 : 0);
   w.epoch = take(m.tp_size > 1 ? 256 : 0);
-  w.pstep = take(m.persistent ? pstep_workspace_bytes(m) : 0);
   w.total = off;
   return w;
 }
@@ -97,7 +96,6 @@ struct Engine {
   cudaGraphExec_t exec = nullptr;
   int launches = 0;
   bool ss_valid = false;  // the residual stream's per-tile sums of squares in h_ss are current
-  PStep* ps = nullptr;    // the persistent-kernel form of the step, when the model asked for it
   unsigned long long* peer_slots[TP_MAX] = {};  // tensor parallelism by peer stores: every rank's exchange buffer
   TpPeer cur_peer = {};                          // where the next EPI_PARTIAL_PEER projection writes
   const void* next_touch[3] = {nullptr, nullptr, nullptr};  // small arrays the next projection asks the L2 for (then cleared)
@@ -607,10 +605,6 @@ struct Engine {
   }
 
   int step(cudaStream_t s) {
-    if (ps) {
-      launches = 1;
-      return pstep_launch(ps, s);
-    }
     if (peer()) {  // the ranks exchange by peer stores inside the kernels: the whole step is one launch sequence
       for (int seg = 0; seg < num_segments(); ++seg)
         if (int rc = step_segment(seg, s)) return rc;
@@ -698,11 +692,6 @@ size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc) {
   return plan(*desc).total;
 }
 
-size_t dfb_engine_weight_stream_bytes(const dfb_model_desc* desc) {
-  if (!desc || (desc->num_layers && !desc->layers_host) || !pstep_eligible(*desc)) return 0;
-  return pstep_stream_bytes(*desc);
-}
-
 int dfb_engine_create(const dfb_model_desc* desc, void** engine_out) {
   if (!desc || !engine_out) {
     set_error("dfb_engine_create: null argument");
@@ -747,14 +736,6 @@ int dfb_engine_create(const dfb_model_desc* desc, void** engine_out) {
       }
     e->m.tp_peer_slots = nullptr;  // copied; the caller's array need not outlive creation
   }
-  if (desc->persistent) {
-    const int rc = pstep_create(e->m, e->at(w.pstep), desc->weight_stream, desc->weight_stream_bytes, &e->ps, nullptr);
-    if (rc) {
-      delete e;
-      return rc;
-    }
-    pstep_set_status(e->ps, (int*)e->at(w.status));
-  }
   *engine_out = e;
   return DFB_OK;
 }
@@ -764,7 +745,6 @@ int dfb_engine_destroy(void* engine) {
   if (!e) return DFB_OK;
   if (e->exec) cudaGraphExecDestroy(e->exec);
   if (e->graph) cudaGraphDestroy(e->graph);
-  if (e->ps) pstep_destroy(e->ps);
   delete e;
   return DFB_OK;
 }
@@ -889,25 +869,6 @@ int dfb_engine_status(void* engine, int* status_host, void* stream) {
     return DFB_ERR_CUDA;
   }
   return DFB_OK;
-}
-
-int dfb_engine_trace_layer(void* engine, int layer) {
-  Engine* e = (Engine*)engine;
-  if (!e || !e->ps) {
-    set_error("dfb_engine_trace_layer: not a persistent engine");
-    return DFB_ERR_ARG;
-  }
-  pstep_set_trace(e->ps, e->at(e->ws.pstep), e->m, layer);
-  return DFB_OK;
-}
-
-int dfb_engine_read_trace(void* engine, int64_t* out_host, int max_values, void* stream) {
-  Engine* e = (Engine*)engine;
-  if (!e || !e->ps || !out_host) {
-    set_error("dfb_engine_read_trace: not a persistent engine, or null buffer");
-    return -1;
-  }
-  return pstep_read_trace(e->ps, (long long*)out_host, max_values, (cudaStream_t)stream);
 }
 
 int dfb_engine_set_prefetch_distance(void* engine, int distance) {

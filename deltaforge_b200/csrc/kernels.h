@@ -299,20 +299,3 @@ int launch_bump(unsigned* counter, cudaStream_t s);
 
 }  // namespace dfb
 
-struct dfb_model_desc;
-
-namespace dfb {
-
-// The whole batch-1 step as one persistent cooperative kernel (persistent_step.cu).
-struct PStep;
-bool pstep_eligible(const dfb_model_desc& m);
-size_t pstep_workspace_bytes(const dfb_model_desc& m);  // activation exchange buffers and tables; zeroed by the caller
-size_t pstep_stream_bytes(const dfb_model_desc& m);     // the re-packed per-CTA weight streams
-int pstep_create(const dfb_model_desc& m, void* ws, void* stream_mem, size_t stream_bytes, PStep** out, cudaStream_t stream);
-void pstep_set_status(PStep* ps, int* status);
-void pstep_set_trace(PStep* ps, void* ws, const dfb_model_desc& m, int layer);
-int pstep_read_trace(PStep* ps, long long* out_host, int max_values, cudaStream_t stream);
-int pstep_launch(PStep* ps, cudaStream_t stream);
-void pstep_destroy(PStep* ps);
-
-}  // namespace dfb

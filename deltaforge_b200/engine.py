@@ -264,7 +264,6 @@ class DecodeEngine:
         *,
         attn_splits: int | None = None,
         math: int = MATH_FAST,
-        persistent: bool = False,
         tp_size: int = 1,
         tp_rank: int = 0,
         tp_peer_slots: list[int] | None = None,
@@ -274,9 +273,7 @@ class DecodeEngine:
         """``prefetch_distance``: how many projections ahead the kernels of a batch-1 step ask the L2 cache for
         weights (``dfb_engine_set_prefetch_distance``; ``None`` keeps the library's default, 0 switches it off).
         ``tensor_core_gemv``: batch 1 runs the layer projections on the integer tensor-core instruction, from one more
-        re-packed copy of each weight (off: the dp4a kernels on the ``k8`` copy).
-        ``persistent``: run the step as one persistent cooperative kernel (batch 1, FAST arithmetic,
-        group-128 weights; other shapes are refused by ``dfb_engine_create``) instead of a graph of kernels."""
+        re-packed copy of each weight (off: the dp4a kernels on the ``k8`` copy)."""
         cfg = weights.config
         self.config, self.weights, self.cache = cfg, weights, cache
         self.batch, self.max_seq = cache.batch_size, cache.max_seq_len
@@ -300,12 +297,12 @@ class DecodeEngine:
             k, n = qw.in_features, qw.out_features
             # the re-packed copy serves the batch-1 streaming kernels and the tensor-core product (8 rows and more)
             wants_k8 = k % 128 == 0 and (self.batch == 1 or self.batch >= 8)
-            if qw.k8 is None and not persistent and wants_k8 and qw.group_size == 128 and n % 4 == 0:
+            if qw.k8 is None and wants_k8 and qw.group_size == 128 and n % 4 == 0:
                 from . import ops  # the re-packed copy the streaming GEMV reads; made once per weight
 
                 qw.k8 = ops.int4_repack_k8(qw.qweight)
             k8 = qw.k8.data_ptr() if qw.k8 is not None else None
-            wants_mma = tensor_core_gemv and layer_sized and self.batch == 1 and not persistent and math == MATH_FAST
+            wants_mma = tensor_core_gemv and layer_sized and self.batch == 1 and math == MATH_FAST
             if wants_mma and qw.group_size == 128 and k % 128 == 0 and (qw.mma is None or qw.mma_pair != pair):
                 from . import ops
 
@@ -352,14 +349,6 @@ class DecodeEngine:
         if tp_peer_slots is not None:
             self._peer_array = (C.c_void_p * len(tp_peer_slots))(*tp_peer_slots)
             m.tp_peer_slots = C.cast(self._peer_array, C.POINTER(C.c_void_p))
-        m.persistent = int(persistent)
-        self.persistent = bool(persistent)
-        if persistent:
-            sbytes = self.lib.dfb_engine_weight_stream_bytes(C.byref(m))
-            if sbytes == 0:
-                raise ValueError("the persistent step supports batch 1 with group-128 int4 weights and 256-wide attention heads only")
-            self.weight_stream = torch.empty(sbytes, dtype=torch.uint8, device=dev)
-            m.weight_stream, m.weight_stream_bytes = self.weight_stream.data_ptr(), sbytes
         nbytes = self.lib.dfb_engine_workspace_bytes(C.byref(m))
         self.workspace = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=dev)
         m.workspace, m.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()

@@ -109,14 +109,14 @@ def _engine_for(model, cache) -> DecodeEngine:
             )
         eng = DecodeEngine(
             model.__dict__["_dfb200_weights"], cache, attn_splits=model.__dict__.get("_dfb200_attn_splits"),
-            math=model.__dict__.get("_dfb200_math", MATH_FAST), persistent=model.__dict__.get("_dfb200_persistent", False),
+            math=model.__dict__.get("_dfb200_math", MATH_FAST),
         )  # fmt: skip
         engines[key] = eng
     return eng
 
 
 def install_b200_decode_step(
-    model, entry=None, *, attn_splits: int | None = None, math: int = MATH_FAST, scale_dtype=None, persistent: bool = False
+    model, entry=None, *, attn_splits: int | None = None, math: int = MATH_FAST, scale_dtype=None
 ) -> None:
     """Replace the single-token forward of ``model`` with the captured CUDA decode step.
 
@@ -156,7 +156,6 @@ def install_b200_decode_step(
     model.__class__ = B200DecodeStepModel
     model.__dict__["_dfb200_attn_splits"] = attn_splits
     model.__dict__["_dfb200_math"] = math
-    model.__dict__["_dfb200_persistent"] = persistent
     model.__dict__["_dfb200_scale_dtype"] = scale_dtype
     setattr(model, FLAG_STEP, True)
 

@@ -325,13 +325,6 @@ typedef struct dfb_model_desc {
   size_t workspace_bytes;
   int32_t attn_splits;
   int32_t math;
-  /* 1: run the step as one persistent kernel (batch 1, group-128 weights, head dim 256, FAST arithmetic;
-   * dfb_engine_create refuses other shapes). It streams the weights from `weight_stream`, a buffer of
-   * dfb_engine_weight_stream_bytes() bytes (128-byte aligned) that dfb_engine_create fills from the
-   * `packed` / `scale` tensors of every dfb_linear; those tensors are not read afterwards. */
-  int32_t persistent;
-  void* weight_stream;
-  size_t weight_stream_bytes;
   /* Tensor parallelism: > 1 says this engine holds one rank's shard (its heads, its slice of the MLP and of
    * the vocabulary; all shapes above are the local ones). The projections that end each half of a layer are
    * sharded along K: they leave fp32 partial sums [batch, hidden] in dfb_engine_partial_buffer() instead of
@@ -355,8 +348,6 @@ typedef struct dfb_model_desc {
 } dfb_model_desc;
 
 size_t dfb_engine_workspace_bytes(const dfb_model_desc* desc);
-/* Bytes of `weight_stream` for a persistent engine on the current device (0 if the shape is not supported). */
-size_t dfb_engine_weight_stream_bytes(const dfb_model_desc* desc);
 
 /* One engine = one model replica's decode step: ReferenceModel.forward at seq_len 1 plus the argmax of
  * greedy_decode (src/deltaforge/reference.py:779-817, src/deltaforge/model.py:141-147). */
@@ -385,14 +376,6 @@ int dfb_engine_decode_host(void* engine, const int64_t* tokens_host, int steps, 
 /* Wait for `stream` and read the engine's status word: 0, or the code a kernel recorded when one of its
  * bounded waits (on a shared-memory barrier fed by asynchronous copies) gave up instead of hanging. */
 int dfb_engine_status(void* engine, int* status_host, void* stream);
-/* Diagnostics of a persistent engine: record device timestamps (ns, %globaltimer) at the phase boundaries of
- * layer `layer` (-1 switches it off) in steps launched afterwards (not in a graph captured before), and read
- * them back: out_host receives [CTAs][32] values, the return value is how many were written (-1 on error).
- * Slots: 0 start, 1 layer start, 2 x built, 3 input projection, 15 attention partial, 4 mixer, 5 x built,
- * 6 output projection, 7 residual gathered, 8 x built, 9 gate|up, 10 x built, 11 down, 12 residual gathered,
- * 16 last layer done, 17 LM head done. */
-int dfb_engine_trace_layer(void* engine, int layer);
-int dfb_engine_read_trace(void* engine, int64_t* out_host, int max_values, void* stream);
 /* How far ahead the kernels of a batch-1 step ask the L2 cache for weights: every launch requests, a slice
  * per CTA, the int4 words and scales of the projection `distance` GEMVs after the one it runs (or precedes),
  * so HBM keeps streaming while the kernels work through their dependent latencies. 0 (the default) switches it

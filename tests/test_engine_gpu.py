@@ -127,10 +127,10 @@ def qwen_width_config(layers=4, vocab=4096) -> ModelConfig:
     )  # fmt: skip
 
 
-@pytest.mark.parametrize("math,persistent", [(E.MATH_FAST, False), (E.MATH_EXACT, False), (E.MATH_FAST, True)])
-def test_full_width_layers_match_oracle(math, persistent):
+@pytest.mark.parametrize("math", [E.MATH_FAST, E.MATH_EXACT])
+def test_full_width_layers_match_oracle(math):
     cfg = qwen_width_config()
-    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=4, max_seq=64, math=math, persistent=persistent)
+    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=4, max_seq=64, math=math)
     scale = ref.float().std().item()
     diff = (ref.float() - got.float()).abs()
     err = diff.max().item()
@@ -152,8 +152,8 @@ def test_full_width_layers_match_oracle(math, persistent):
     assert_caches_close(oc, cc, atol_state=2e-2 if math == E.MATH_EXACT else 2e-1)
     eng = cand.decode_engine(cc)
     eng.check_status()
-    # embed, 5 launches per layer of either kind, head + argmax + advance; or the one persistent kernel
-    assert eng.launches_per_step == (1 if persistent else 1 + 4 * 5 + 3)
+    # embed, 5 launches per layer of either kind, head + argmax + advance
+    assert eng.launches_per_step == 1 + 4 * 5 + 3
 
 
 def test_one_kv_head_shard_with_a_long_cache_takes_128_slices():
@@ -162,7 +162,7 @@ def test_one_kv_head_shard_with_a_long_cache_takes_128_slices():
     import dataclasses
 
     cfg = dataclasses.replace(qwen_width_config(), num_attention_heads=4, num_key_value_heads=1)
-    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=3, max_seq=8448, math=E.MATH_EXACT, persistent=False)
+    ref, got, oc, cc, cand = run_pair(cfg, batch=1, prompt_len=3, steps=3, max_seq=8448, math=E.MATH_EXACT)
     eng = cand.decode_engine(cc)
     assert eng.attn_splits == 128
     eng.check_status()
@@ -250,52 +250,6 @@ def test_graph_replay_equals_plain_launches_and_is_repeatable():
     cache.restore(snap)
     host = eng.decode_host(tok.cpu().pin_memory(), 5)
     assert torch.equal(host.t().to(DEV), on_device)
-
-
-def test_persistent_engine_replays_and_matches_the_graph_engine():
-    """The one-kernel form of the step: graph replay == plain launches, greedy loop == stepping by hand, cache
-    restore between runs (the exchange buffers carry epochs, nothing needs clearing), and its logits within
-    bf16 noise of the multi-kernel engine's on the same weights and cache."""
-    cfg = qwen_width_config(layers=4, vocab=2048)
-    w = synth.random_model_weights(cfg, seed=3, device=DEV, scale_dtype=torch.bfloat16)
-    cache = E.DecodeCache(cfg, 1, 512, device=DEV)
-    synth.fill_cache(cache, 300, seed=5)
-    snap = cache.snapshot()
-    tok = torch.tensor([17], device=DEV)
-    ref_eng = E.DecodeEngine(w, cache)
-    want = [ref_eng.step(tok).clone()]
-    want.append(ref_eng.step(want[0].argmax(-1)).clone())
-    state_want = [t.clone() for t in cache.state_tensors()]
-    cache.restore(snap)
-    eng = E.DecodeEngine(w, cache, persistent=True)
-    assert eng.launches_per_step in (0, 1)
-    plain = [eng.step(tok, graph=False).clone()]
-    plain.append(eng.step(want[0].argmax(-1), graph=False).clone())
-    state_plain = [t.clone() for t in cache.state_tensors()]
-    eng.check_status()
-    cache.restore(snap)
-    graph = [eng.step(tok, graph=True).clone()]
-    graph.append(eng.step(want[0].argmax(-1), graph=True).clone())
-    for a, b in zip(plain, graph):
-        assert torch.equal(a, b)
-    for a, b in zip(state_plain, cache.state_tensors()):
-        assert torch.equal(a, b)
-    scale = want[0].float().std().item()
-    for a, b in zip(want, plain):
-        assert (a.float() - b.float()).abs().max().item() < 6e-2 * scale
-    for a, b in zip(state_want, state_plain):
-        assert (a.float() - b.float()).abs().max().item() <= 2e-2 + 2e-2 * a.float().abs().max().item()
-    cache.restore(snap)
-    by_hand, t = [], tok
-    for _ in range(5):
-        by_hand.append(eng.step(t).argmax(-1))
-        t = by_hand[-1]
-    cache.restore(snap)
-    on_device = eng.decode(tok, 5)
-    assert torch.equal(on_device, torch.stack(by_hand, dim=1))
-    assert cache.seq_len == 305
-    eng.check_status()
-    assert eng.launches_per_step == 1
 
 
 def test_capacity_is_checked_on_the_host():
