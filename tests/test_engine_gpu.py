@@ -214,7 +214,7 @@ def test_long_slices_of_many_sequences_decode_position_after_position_with_a_cle
         worst = max(worst, time.perf_counter() - t0)
     eng.check_status()
     assert bool(torch.isfinite(eng.logits.float()).all())
-    assert worst < 0.06, f"a step took {worst * 1e3:.1f} ms"
+    assert worst < 0.1, f"a step took {worst * 1e3:.1f} ms"  # 12 ms when all is well, 149 ms when a wait ran out
 
 
 def test_graph_replay_equals_plain_launches_and_is_repeatable():
